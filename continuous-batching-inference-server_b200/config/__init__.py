@@ -4,11 +4,13 @@ from .registry import (architecture_name, config_from_dict, known_architectures,
 from .gpt2 import GPT2Config
 from .vekedra import VekedraConfig
 from .figotar import FigotarConfig
+from .vatevik import VatevikConfig
 
 for _name in ("GPT2LMHeadModel", "TinyGPT", "gpt2"):
     register_architecture(_name, GPT2Config)
 register_architecture("Vekedra", VekedraConfig)
 register_architecture("Figotar", FigotarConfig)
+register_architecture("Vatevik", VatevikConfig)
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "GPT2Config", "VekedraConfig", "FigotarConfig", "architecture_name",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "GPT2Config", "VekedraConfig", "FigotarConfig", "VatevikConfig", "architecture_name",
            "config_from_dict", "known_architectures", "load_config", "register_architecture"]

@@ -47,7 +47,7 @@ __global__ void add_rmsnorm_kernel(float* x, const TD* delta, int delta_ld, cons
     row[c] = v;
     ss += v * v;
   }
-  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+  const float inv = w ? 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps) : 1.f;      // no weight: the rows go on as they are
   const bool write_x = rows == nullptr && drow != nullptr;
   TO* orow = out ? out + (size_t)r * d : nullptr;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
@@ -138,7 +138,7 @@ add_rmsnorm_reg_kernel(float* x, const TD* delta, int delta_ld, const float* __r
       ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
     }
   }
-  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+  const float inv = w ? 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps) : 1.f;      // no weight: the rows go on as they are
   const bool write_x = rows == nullptr && drow != nullptr;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {

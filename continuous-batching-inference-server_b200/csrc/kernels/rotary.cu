@@ -6,6 +6,11 @@
 //   Source and destination may be different buffers with different strides between heads (a head's rotated part is
 //   moved to its place among the columns the attention kernel reads); entries beyond `dims` up to `width` are copied.
 //   head_gate_mul: out[r, h, :] = x[r, h, :] * sigmoid(gate[r, h]), one number per row and head.
+//   qk_prepare: what stands between a projection q | k | v and attention, in place, one pass over a row: a
+//   root-mean-square norm over ALL of q at once and over ALL of k at once (weights as wide as the projections, not one
+//   per head), then the rotation of every head of q and k, and values blended with another layer's values of the same
+//   token: v <- (1 - lambda) v + lambda v_other.  Each of the three steps is optional.
+//   blend_rows: the last of them alone.
 #include "common.cuh"
 
 namespace cbis {
@@ -57,9 +62,130 @@ __global__ void head_gate_mul_kernel(const TT* x, int x_ld, const TG* gate, int 
   }
 }
 
+// One block per row.  q and k wait in shared memory (d_q + d_k floats) between the sums of squares and the rotation;
+// a value is rounded once, after norm, weight and rotation.
+template <typename TT>
+__global__ void qk_prepare_kernel(TT* buf, int ld, int q_off, int q_heads, int k_off, int k_heads, int width,
+                                  const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                  const int* positions, const float* __restrict__ freqs, int dims, int v_off, int d_v,
+                                  const TT* v_other, int v_other_ld, float lambda) {
+  extern __shared__ float row[];
+  __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  TT* b = buf + (size_t)r * ld;
+  const int d_q = q_heads * width, d_k = k_heads * width;
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < d_q + d_k; c += blockDim.x) {
+    const float v = to_f32(c < d_q ? b[q_off + c] : b[k_off + c - d_q]);
+    row[c] = v;
+    if (c < d_q) sq += v * v;
+    else sk += v * v;
+  }
+  float inv_q = 1.f, inv_k = 1.f;
+  if (q_w) inv_q = 1.0f / sqrtf(block_sum(sq, red) / (float)d_q + eps);
+  if (k_w) inv_k = 1.0f / sqrtf(block_sum(sk, red) / (float)d_k + eps);
+  __syncthreads();
+  const float p = (float)positions[r];
+  const int half = dims / 2, per_head = half + (width - dims);      // pairs, then entries that pass unrotated
+  for (int u = threadIdx.x; u < (q_heads + k_heads) * per_head; u += blockDim.x) {
+    const int h = u / per_head, i = u % per_head;
+    const bool is_q = h < q_heads;
+    const int c0 = is_q ? h * width : (h - q_heads) * width;       // the head's first column within its projection
+    const float* src = row + (is_q ? 0 : d_q) + c0;
+    const float* w = is_q ? q_w : k_w;
+    const float inv = is_q ? inv_q : inv_k;
+    TT* dst = b + (is_q ? q_off : k_off) + c0;
+    if (i < half) {
+      float x0 = src[i] * inv, x1 = src[i + half] * inv;
+      if (w) {
+        x0 *= w[c0 + i];
+        x1 *= w[c0 + i + half];
+      }
+      float sn, cs;
+      sincosf(p * freqs[i], &sn, &cs);
+      from_f32(dst[i], x0 * cs - x1 * sn);
+      from_f32(dst[i + half], x1 * cs + x0 * sn);
+    } else {
+      const int c = dims + (i - half);
+      float x0 = src[c] * inv;
+      if (w) x0 *= w[c0 + c];
+      from_f32(dst[c], x0);
+    }
+  }
+  if (v_other) {
+    const TT* o = v_other + (size_t)r * v_other_ld;
+    for (int c = threadIdx.x; c < d_v; c += blockDim.x)
+      from_f32(b[v_off + c], (1.0f - lambda) * to_f32(b[v_off + c]) + lambda * to_f32(o[c]));
+  }
+}
+
+// out[r, c] = (1 - lambda) a[r, c] + lambda b[r, c]
+template <typename TT>
+__global__ void blend_rows_kernel(const TT* a, int a_ld, const TT* b, int b_ld, TT* out, int out_ld, float lambda,
+                                  int rows, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)rows * n;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / n;
+    const int c = (int)(i % n);
+    from_f32(out[r * out_ld + c], (1.0f - lambda) * to_f32(a[r * a_ld + c]) + lambda * to_f32(b[r * b_ld + c]));
+  }
+}
+
 }  // namespace cbis
 
 using namespace cbis;
+
+CBIS_EXPORT int cbis_qk_prepare_max_width() { return 200 * 1024 / 4 - 64; }
+
+// buf [rows, ld] of the compute type, changed in place: q at columns q_off.. (q_heads x width), k at k_off..
+// (k_heads x width), v at v_off.. (d_v).  q_w / k_w (may be null): the norms' weights, q_heads * width and
+// k_heads * width wide; freqs (null with dims 0): dims / 2 numbers; v_other (may be null): [rows, v_other_ld].
+CBIS_EXPORT int cbis_qk_prepare(void* buf, int ld, int q_off, int q_heads, int k_off, int k_heads, int width,
+                                const float* q_w, const float* k_w, float eps, const int* positions, const float* freqs,
+                                int dims, int v_off, int d_v, const void* v_other, int v_other_ld, float lambda, int rows,
+                                int dtype, void* stream) {
+  if (rows <= 0) return CBIS_OK;
+  if (q_heads < 0 || k_heads < 0 || width <= 0 || dims < 0 || dims > width || dims % 2 || (dims > 0 && !freqs))
+    return CBIS_ERR_BAD_SIZE;
+  const long long n = (long long)(q_heads + k_heads) * width;
+  if (n > cbis_qk_prepare_max_width()) return CBIS_ERR_BAD_SIZE;
+  const size_t smem = (size_t)n * sizeof(float);
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  cudaStream_t st = (cudaStream_t)stream;
+#define CBIS_QKP(TT)                                                                                                  \
+  do {                                                                                                                \
+    if (smem > 48 * 1024)                                                                                             \
+      cudaFuncSetAttribute(qk_prepare_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+    return (int)launch_pdl(qk_prepare_kernel<TT>, dim3(rows), dim3(threads), smem, st, (TT*)buf, ld, q_off, q_heads,  \
+                           k_off, k_heads, width, q_w, k_w, eps, positions, freqs, dims, v_off, d_v,                  \
+                           (const TT*)v_other, v_other_ld, lambda);                                                   \
+  } while (0)
+  if (dtype == CBIS_F32) CBIS_QKP(float);
+  if (dtype == CBIS_BF16) CBIS_QKP(__nv_bfloat16);
+#undef CBIS_QKP
+  return CBIS_ERR_BAD_DTYPE;
+}
+
+CBIS_EXPORT int cbis_blend_rows(const void* a, int a_ld, const void* b, int b_ld, void* out, int out_ld, float lambda,
+                                int rows, int n, int dtype, void* stream) {
+  if (rows <= 0 || n <= 0) return CBIS_OK;
+  const size_t total = (size_t)rows * n;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == CBIS_F32)
+    return (int)launch_pdl(blend_rows_kernel<float>, dim3((int)blocks), dim3(256), 0, st, (const float*)a, a_ld,
+                           (const float*)b, b_ld, (float*)out, out_ld, lambda, rows, n);
+  if (dtype == CBIS_BF16)
+    return (int)launch_pdl(blend_rows_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, st,
+                           (const __nv_bfloat16*)a, a_ld, (const __nv_bfloat16*)b, b_ld, (__nv_bfloat16*)out, out_ld,
+                           lambda, rows, n);
+  return CBIS_ERR_BAD_DTYPE;
+}
 
 CBIS_EXPORT int cbis_rope_rows(const void* src, int src_ld, int src_col0, int src_head_stride, void* dst, int dst_ld,
                                int dst_col0, int dst_head_stride, const int* positions, int rows, int heads, int width,

@@ -914,6 +914,69 @@ def matrix_memory(qkv, q_off, k_off, v_off, gates, i_bias, f_bias, cap, q_scale,
     _check(st, "matrix_memory", f"segments={n_segments} heads={heads} dim={dim} v_dim={v_dim}")
 
 
+RETENTION_MAX_DIM = 512                                  # the widest key of the retention kernel (cbis_retention_max_dim())
+QK_PREPARE_MAX_WIDTH = 200 * 1024 // 4 - 64              # q and k of a row together, in entries (cbis_qk_prepare_max_width())
+USE_QK_PREPARE = __import__("os").environ.get("CBIS_QK_PREPARE", "1") != "0"   # 0: norm, rotation and blending before attention run as kernels of their own
+
+
+def retention(qkv, q_off, k_off, v_off, positions, freqs, rot_dims, k_scale, one_minus_decay, state, seg_slot, cu_rows,
+              n_segments, heads, dim, v_dim, y, max_seg_rows: int = 0):
+    """Retention over every segment's rows, from and into the requests' states: per head S <- decay S + k v^T,
+    y = S^T q, after the first ``rot_dims`` entries of q and k were rotated in pairs (entry i with i + rot_dims/2) by
+    position * freqs[i] and k was multiplied by ``k_scale``.  ``qkv``: the compute type, q | k | v at their column
+    offsets; ``one_minus_decay``: 32-bit ``[heads]``, 1 - decay per head; ``y``: 32-bit ``[T, heads * v_dim]``;
+    ``state``: 32-bit ``[slots, heads * v_dim * dim]``; ``max_seg_rows``: the step's longest segment if known."""
+    _need_cuda(qkv, positions, freqs, one_minus_decay, state, seg_slot, cu_rows, y)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and positions.dtype == torch.int32 and positions.shape[0] >= T
+    assert y.dtype == torch.float32 and y.stride(1) == 1 and y.shape == (T, heads * v_dim)
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= heads * v_dim * dim
+    assert one_minus_decay.dtype == torch.float32 and one_minus_decay.numel() == heads and one_minus_decay.is_contiguous()
+    assert rot_dims == 0 or (freqs.dtype == torch.float32 and freqs.numel() >= rot_dims // 2 and freqs.is_contiguous())
+    st = kernels().cbis_retention(_ptr(qkv), c_int(qkv.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), _ptr(positions),
+                                  _ptr(freqs), c_int(rot_dims), c_float(k_scale), _ptr(one_minus_decay), _ptr(state),
+                                  ctypes.c_longlong(state.stride(0)), _ptr(seg_slot), _ptr(cu_rows), _ptr(y),
+                                  c_int(y.stride(0)), c_int(n_segments), c_int(heads), c_int(dim), c_int(v_dim),
+                                  c_int(dtype_code(qkv.dtype)), _stream(), c_int(int(max_seg_rows)))
+    _check(st, "retention", f"segments={n_segments} heads={heads} dim={dim} v_dim={v_dim} rot_dims={rot_dims}")
+
+
+def qk_prepare(buf, q_off, q_heads, k_off, k_heads, width, q_weight, k_weight, eps, positions, freqs, rot_dims,
+               v_off=0, d_v=0, v_other=None, blend: float = 0.0):
+    """What stands between a projection q | k | v (``buf``, the compute type, changed in place) and attention, in
+    one pass over a row, 32-bit arithmetic, one rounding: all of q (``q_heads`` x ``width`` from column ``q_off``)
+    divided by its root mean square and multiplied by ``q_weight``, the same for all of k (weights None: no norm);
+    every head's first ``rot_dims`` entries rotated in pairs (entry i with i + rot_dims/2) by position * freqs[i]; and
+    with ``v_other`` (``[rows, d_v]``) the ``d_v`` columns from ``v_off`` become (1 - blend) v + blend v_other."""
+    _need_cuda(buf, q_weight, k_weight, positions, freqs, v_other)
+    rows = buf.shape[0]
+    assert buf.stride(1) == 1 and positions.dtype == torch.int32 and positions.shape[0] >= rows
+    assert q_off + q_heads * width <= buf.shape[1] and k_off + k_heads * width <= buf.shape[1]
+    for w, n in ((q_weight, q_heads * width), (k_weight, k_heads * width)):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == n and w.is_contiguous())
+    assert rot_dims == 0 or (freqs.dtype == torch.float32 and freqs.numel() >= rot_dims // 2 and freqs.is_contiguous())
+    assert v_other is None or (v_other.dtype == buf.dtype and v_other.stride(1) == 1 and v_other.shape == (rows, d_v)
+                               and v_off + d_v <= buf.shape[1])
+    st = kernels().cbis_qk_prepare(_ptr(buf), c_int(buf.stride(0)), c_int(q_off), c_int(q_heads), c_int(k_off), c_int(k_heads),
+                                   c_int(width), _ptr(q_weight), _ptr(k_weight), c_float(eps), _ptr(positions), _ptr(freqs),
+                                   c_int(rot_dims), c_int(v_off), c_int(d_v), _ptr(v_other),
+                                   c_int(v_other.stride(0) if v_other is not None else 0), c_float(blend), c_int(rows),
+                                   c_int(dtype_code(buf.dtype)), _stream())
+    _check(st, "qk_prepare", f"rows={rows} heads={q_heads}/{k_heads} width={width} rot_dims={rot_dims}")
+
+
+def blend_rows(a, b, blend: float, out):
+    """out = (1 - blend) a + blend b element by element (32-bit arithmetic, one rounding); ``[rows, n]`` of one type,
+    views with unit column stride are fine."""
+    _need_cuda(a, b, out)
+    rows, n = a.shape
+    assert b.shape == a.shape and out.shape == a.shape and a.dtype == b.dtype == out.dtype
+    assert a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1
+    st = kernels().cbis_blend_rows(_ptr(a), c_int(a.stride(0)), _ptr(b), c_int(b.stride(0)), _ptr(out), c_int(out.stride(0)),
+                                   c_float(blend), c_int(rows), c_int(n), c_int(dtype_code(a.dtype)), _stream())
+    _check(st, "blend_rows", f"rows={rows} n={n}")
+
+
 _limits = {}
 
 

@@ -139,6 +139,7 @@ class Model:
     # ---- one step ------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor:
         """Logits (float32 ``[R, vocab]``) at ``ctx.logit_rows`` for the rows of this step."""
+        ctx.shared = {}      # what layers hand to later layers within one step
         x = self.embedding.forward(ctx, self.position)
         pending = None
         sched = self.spec.schedule

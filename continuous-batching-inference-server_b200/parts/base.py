@@ -179,6 +179,11 @@ class Norm(Part):
         own kernel asks for them), else None."""
         return None
 
+    def as_rmsnorm(self):
+        """(weight, eps, offset) if this norm is exactly y = x / sqrt(mean(x^2) + eps) * (offset + weight) over rows
+        of ``self.width`` (another norm that applies it in its own pass asks for them), else None."""
+        return None
+
 
 class PositionEncoding(Part):
     """Position information.  ``embed`` makes the residual stream of a step from its tokens

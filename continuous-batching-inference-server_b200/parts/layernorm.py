@@ -44,17 +44,26 @@ class LayerNorm(Norm):
 
 class NoNorm(Norm):
     """No normalisation: adds what is pending to the residual stream and hands the rows on in the
-    compute dtype (for a model without a final norm)."""
+    compute dtype (for a model without a final norm, and for a part that reads the stream as it is).  What is pending
+    may name a root-mean-square norm of its own (a layer that normalises a part's RESULT): it is applied in the same
+    pass over the row."""
 
     def __init__(self, width: int):
         self.width = int(width)
         if not 0 < self.width <= ops.NORM_MAX_WIDTH:
             raise ValueError(f"width {self.width} is outside 1..{ops.NORM_MAX_WIDTH}, the widest row the kernel takes")
 
+    def takes_post(self, post):
+        return (getattr(post, "width", None) == self.width and self.width <= ops.RMS_RESIDUAL_MAX_WIDTH
+                and post.as_rmsnorm() is not None)
+
     def forward(self, ctx, x, delta: Optional[Delta], rows=None, out_dtype=None):
         n = rows.shape[0] if rows is not None else x.shape[0]
         delta = settle_delta(ctx, self, delta)
         out = torch.empty((n, self.width), dtype=out_dtype or ctx.dtype, device=x.device)
+        if delta is not None and delta.post is not None:      # x += post(delta); the rows go on as they are
+            ops.add_rmsnorm(x, delta.value, delta.bias, delta.post.as_rmsnorm(), None, 0.0, 0.0, out, rows)
+            return out
         ops.add_layernorm(x, delta.value if delta else None, delta.bias if delta else None, None, None, 0.0, out, rows)
         return out
 

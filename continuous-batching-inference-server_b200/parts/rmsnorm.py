@@ -32,6 +32,9 @@ class RMSNorm(Norm):
     def load(self, prefix, tensors, dtype, device):
         self.weight = self._vector(tensors[prefix + self.name], device)
 
+    def as_rmsnorm(self):
+        return (self.weight, self.eps, self.offset) if self.weight is not None else None
+
     def takes_post(self, post):
         return isinstance(post, RMSNorm) and post.width == self.width and post.weight is not None
 
