@@ -143,10 +143,9 @@ class VatevikConfig:
         for layer in self.layers:
             m = layer.mixer_dict()
             base, dims, stretch = m.pop("rot_base"), m.pop("rot_dims"), m.pop("rot_stretch")
-            if dims:
-                m["rot"] = {"base": base, "dims": dims}
-                if stretch is not None:
-                    m["rot"]["scaling"] = dict(zip(("factor", "low", "high", "original"), stretch))
+            m["rot"] = {"base": base, "dims": dims}
+            if stretch is not None:
+                m["rot"]["scaling"] = dict(zip(("factor", "low", "high", "original"), stretch))
             if "decay" in m:
                 m["decay"] = list(m["decay"])
             out.append({"type": layer.type, "mixer": m, "mlp": layer.mlp_dict()})
