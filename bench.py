@@ -115,13 +115,14 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl", "batching", "vekedra", "figotar"],
+    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl", "batching", "vekedra", "figotar", "vatevik"],
                     help="1.3b: the default measurement; 6.7b: batch-64 decode at context 2,048; "
                          "xl: 64 mixed requests through the scheduler (prompts 32-768, 256 outputs each); "
                          "batching: the reference's own workload at the reference's own sizes (both --impl arms); "
                          "vekedra: prefill and decode of the Vekedra design at two layer sizes beside the GPT-2 style model "
                          "of equal width and depth, and its own kernels one by one against their bytes; "
-                         "figotar: the same for the Figotar design, beside Vekedra and the GPT-2 style model")
+                         "figotar: the same for the Figotar design, beside Vekedra and the GPT-2 style model; "
+                         "vatevik: the same for the Vatevik design, beside Figotar and the GPT-2 style model")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
@@ -158,6 +159,8 @@ def main() -> int:
         return vekedra_workload(args, cb, torch)
     if args.config == "figotar":
         return figotar_workload(args, cb, torch)
+    if args.config == "vatevik":
+        return vatevik_workload(args, cb, torch)
     if args.config == "6.7b":
         args.skip_points = True
         args.batch = args.batch or 64
@@ -623,6 +626,207 @@ def vekedra_kernels(torch, ops, pk):
             flops = 2.0 * rows * top * 3 * F * W
             us = out[f"routed_feed_forward_{tag}"]["us"]
             out[f"routed_feed_forward_{tag}"]["frac_of_bf16_peak"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
+    return out
+
+
+def vatevik_sizes(width, layers):
+    """A Vatevik configuration with layers of the sizes a model of this width would have: attention (grouped
+    key/value heads, stretched rotation, blended values) and retention (half as many heads, values twice as wide as
+    keys, decays 1 - 2^-(5 + h)) in turn; every layer with a gated feed-forward."""
+    big = width >= 2048
+    hd = 128 if big else 64
+    heads = width // hd
+    att = {"dim": hd, "heads": heads, "kv_heads": max(1, heads // 4),
+           "rot": {"base": 500000.0, "dims": hd, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+           "scale": hd ** -0.5, "v_mix": True, "vdim": hd}
+    ret = {"decay": [1.0 - 2.0 ** (-5 - h) for h in range(heads // 2)], "dim": hd, "heads": heads // 2,
+           "rot": {"base": 10000.0, "dims": hd}, "vdim": 2 * hd}
+    mlp = {"kind": "dense", "ff": 8 * width // 3 // 64 * 64}
+    out = []
+    for i in range(layers):
+        kind = ("attention", "retention")[i % 2]
+        out.append({"type": kind, "mixer": dict(att if kind == "attention" else ret), "mlp": dict(mlp)})
+    return {"architecture": "Vatevik", "embedding": {"scale": 8.0}, "layers": out, "logit_scale": 0.25, "logit_softcap": 30.0,
+            "norm": {"eps": 1e-6}, "vocab": 32000, "width": width}
+
+
+def vatevik_workload(args, cb, torch) -> int:
+    """Prefill (one 2,048-token prompt in one step) and decode (batch 8 from context 1,024, the captured step with
+    argmax on the device) of the Vatevik design at two layer sizes, each beside Figotar (the closest model: norms on
+    the parts' results, a matrix recurrence walked row by row, attention with a sink) and the GPT-2 style model of
+    equal width and depth; then the design's own kernels alone, at the larger size, beside the like kernels of
+    those models."""
+    from cbis_b200.kernels import ops
+    pk = peaks()
+    P, T, B = 2048, 2048, args.batch or 8
+    steps, warm = min(args.steps, 128), max(3, min(args.warmup, 8))
+    layers = args.layers or 8
+    gen = torch.Generator().manual_seed(0)
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    for width in (1024, 2048):
+        gpt = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=layers, n_embd=width, n_head=16,
+                   n_inner=4 * width, vocab_size=32000, n_positions=P, activation_function="gelu",
+                   layer_norm_epsilon=1e-5, tie_word_embeddings=False)
+        sizes[f"width_{width}"] = {name: measure_model(args, cb, torch, pk, cfgd, 32000, B, P, T, steps, warm, gen)
+                                   for name, cfgd in (("vatevik", vatevik_sizes(width, layers)),
+                                                      ("figotar", figotar_sizes(width, layers)), ("gpt2_style", gpt))}
+    clocks = sampler.stop()
+    line = {"metric": f"Vatevik prefill and decode tokens/s beside Figotar and the GPT-2 style model of equal width and "
+                      f"depth ({layers} layers, batch {B}, prompt {T})", "unit": "tokens/s", "n_gpus": 1, "impl": "b200",
+            "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)", "higher_is_better": True,
+            "value": sizes["width_2048"]["vatevik"]["decode_tokens_per_s"], "sizes": sizes,
+            "kernels": vatevik_kernels(torch, ops, pk), "clocks": clocks, "peaks": pk}
+    print(json.dumps(line))
+    return 0
+
+
+def graph_timer(torch, pk, out):
+    """``timed(make, nbytes, name, flops)``: microseconds of a kernel alone, replayed from a CUDA graph over buffers that
+    rotate, with its bytes over its time as a fraction of the measured copy bandwidth."""
+    def timed(make, nbytes, name, flops=0.0, reps=20, copies=4):
+        fns = [make() for _ in range(copies)]
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / reps / copies * 1e3
+        out[name] = {"us": round(us, 2), "bytes": int(nbytes), "frac_of_copy_bandwidth": round(nbytes / us / 1e3 / pk["hbm_gbs"], 4)}
+        if flops:
+            out[name]["frac_of_bf16_peak"] = round(flops / us / 1e6 / pk["bf16_tflops"], 4)
+    return timed
+
+
+def vatevik_kernels(torch, ops, pk):
+    """Microseconds of the design's own kernels alone at the layer sizes of width 2,048, with the bytes each has to move
+    over its time as a fraction of the measured copy bandwidth, each beside the like kernel of the closest model at
+    equal sizes."""
+    bf = torch.bfloat16
+    out = {}
+    timed = graph_timer(torch, pk, out)
+    W, H, D, V = 2048, 8, 128, 256                 # retention of width 2,048: 8 heads of 128 x 256 (the closest model's memory too)
+    nh, nkv, hd = 16, 4, 128                       # attention of that width
+    freqs = (10000.0 ** (-2.0 * torch.arange(D // 2, dtype=torch.float64) / D)).float().cuda()
+    for rows, segs, tag in ((2048, 1, "prefill_2048"), (8, 8, "decode_8")):
+        per = rows // segs
+        seg_slot = torch.arange(segs, dtype=torch.int32, device="cuda")
+        cu = torch.arange(0, rows + 1, per, dtype=torch.int32, device="cuda")
+        pos = (torch.arange(rows, dtype=torch.int32, device="cuda") % per) + (1024 if segs > 1 else 0)
+
+        def retention():
+            qkv = (torch.randn(rows, 2 * H * D + 2 * H * V, device="cuda") * 0.5).to(bf)
+            om = torch.tensor([2.0 ** (-5 - h) for h in range(H)], device="cuda")
+            st = torch.zeros(segs, H * D * V, device="cuda")
+            y = torch.empty(rows, H * V, device="cuda")
+            return lambda: ops.retention(qkv, 0, H * D, 2 * H * D, pos, freqs, D, D ** -0.5, om, st, seg_slot, cu, segs, H, D, V, y,
+                                         max_seg_rows=per)
+        timed(retention, rows * ((2 * H * D + H * V) * 2 + H * V * 4) + 2 * segs * H * D * V * 4, f"retention_{tag}")
+
+        def memory():
+            qkv = (torch.randn(rows, 2 * H * D + 2 * H * V, device="cuda") * 0.5).to(bf)
+            gates = torch.randn(rows, 2 * H, device="cuda")
+            ib, fb = torch.zeros(H, device="cuda"), torch.full((H,), 3.0, device="cuda")
+            st = torch.zeros(segs, ops.matrix_memory_state_floats(H, D, V), device="cuda")
+            y = torch.empty(rows, H * V, device="cuda")
+            return lambda: ops.matrix_memory(qkv, 0, H * D, 2 * H * D, gates, ib, fb, 15.0, D ** -0.5, 1e-6, st, seg_slot, cu,
+                                             segs, H, D, V, y, max_seg_rows=per)
+        timed(memory, rows * ((2 * H * D + H * V) * 2 + H * V * 4) + 2 * segs * H * D * V * 4, f"closest_model_matrix_memory_{tag}")
+
+        def result_norm():
+            x, d = torch.randn(rows, W, device="cuda"), torch.randn(rows, W, device="cuda")
+            wb = torch.ones(W, device="cuda")
+            o = torch.empty(rows, W, dtype=bf, device="cuda")
+            return lambda: ops.add_rmsnorm(x, d, None, (wb, 1e-6, 0.0), None, 0.0, 0.0, o)
+        timed(result_norm, rows * W * (4 + 4 + 4 + 2), f"add_rmsnorm_no_norm_before_{tag}")
+
+        def sandwich():
+            x, d = torch.randn(rows, W, device="cuda"), torch.randn(rows, W, device="cuda")
+            w, wb = torch.zeros(W, device="cuda"), torch.zeros(W, device="cuda")
+            o = torch.empty(rows, W, dtype=bf, device="cuda")
+            return lambda: ops.add_rmsnorm(x, d, None, (wb, 1e-6, 1.0), w, 1e-6, 1.0, o)
+        timed(sandwich, rows * W * (4 + 4 + 4 + 2), f"closest_model_add_rmsnorm_{tag}")
+
+        dq, dk = nh * hd, nkv * hd
+
+        def prepare():
+            buf = torch.randn(rows, dq + 2 * dk, device="cuda").to(bf)
+            other = torch.randn(rows, dk, device="cuda").to(bf)
+            qw, kw = torch.ones(dq, device="cuda"), torch.ones(dk, device="cuda")
+            return lambda: ops.qk_prepare(buf, 0, nh, dq, nkv, hd, qw, kw, 1e-6, pos, freqs, hd, dq + dk, dk, other, 0.5)
+        timed(prepare, rows * (2 * (dq + 2 * dk) + dk) * 2, f"qk_prepare_{tag}")
+
+        def prepare_in_steps():
+            buf = torch.randn(rows, dq + 2 * dk, device="cuda").to(bf)
+            other = torch.randn(rows, dk, device="cuda").to(bf)
+            qw, kw = torch.ones(dq, device="cuda"), torch.ones(dk, device="cuda")
+            q, k, v = buf[:, :dq], buf[:, dq:dq + dk], buf[:, dq + dk:]
+
+            def run():
+                ops.rms_norm(q, qw, 1e-6, q)
+                ops.rms_norm(k, kw, 1e-6, k)
+                ops.rope_rows(buf, 0, hd, buf, 0, hd, pos, nh, hd, hd, freqs)
+                ops.rope_rows(buf, dq, hd, buf, dq, hd, pos, nkv, hd, hd, freqs)
+                ops.blend_rows(v, other, 0.5, v)
+            return run
+        timed(prepare_in_steps, rows * (2 * (dq + 2 * dk) + dk) * 2, f"the_same_in_five_kernels_{tag}")
+
+        def rope_alone():       # the closest model's rotation: one array of rotated key parts
+            buf = torch.randn(rows, dq + dk, device="cuda").to(bf)
+            return lambda: ops.rope_rows(buf, 0, hd, buf, 0, hd, pos, nh + nkv, hd, hd, freqs)
+        timed(rope_alone, rows * 2 * (dq + dk) * 2, f"closest_model_rope_rows_{tag}")
+
+        def gated_norm():
+            y = torch.randn(rows, H * V, device="cuda")
+            z = torch.randn(rows, H * V, device="cuda").to(bf)
+            o = torch.empty(rows, H * V, dtype=bf, device="cuda")
+            return lambda: ops.rms_norm(y, None, 1e-6, o, parts=H, gate=z, gate_act="silu", gate_after=True)
+        timed(gated_norm, rows * H * V * (4 + 2 + 2), f"head_norm_with_gate_{tag}")
+
+    # attention: 16 query heads over 4 key/value heads of 128, all keys, pages of 16, 1 in the denominator
+    ps, ctx_len = 16, 2048
+    pages = ctx_len // ps
+    bt1 = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, pages)
+    cu1 = torch.tensor([0, ctx_len], dtype=torch.int32, device="cuda")
+    zero1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sinks = torch.zeros(nh, device="cuda")
+    keys = ctx_len * (ctx_len + 1) // 2
+    for name, extra in (("attention_prefill_2048_sink", dict(v_head_dim=hd, sinks=sinks)),
+                        ("closest_model_attention_prefill_2048_same_kernel_plain", {})):
+        def prefill():
+            q = torch.randn(ctx_len, nh * hd, device="cuda").to(bf)
+            k, v = (torch.randn(pages, nkv, ps, hd, device="cuda").to(bf) for _ in range(2))
+            o = torch.empty(ctx_len, nh * hd, dtype=bf, device="cuda")
+            return lambda: ops.paged_prefill_bf16(q, k, v, bt1, cu1, zero1, o, 0, 1, ctx_len, nh, nkv, hd, ps, hd ** -0.5, 0, **extra)
+        timed(prefill, ctx_len * (2 * nh + 2 * nkv) * hd * 2, name, flops=4.0 * keys * nh * hd)
+    B = 8
+    btB = torch.arange(B * pages, dtype=torch.int32, device="cuda").view(B, pages)
+    row_seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    posB = torch.full((B,), ctx_len - 1, dtype=torch.int32, device="cuda")
+    slot_map = (btB[:, -1] * ps + ps - 1).contiguous()
+    for name, extra in (("attention_decode_8_sink", dict(v_head_dim=hd, sinks=sinks)),
+                        ("closest_model_attention_decode_8_tensor_core_form_plain", {})):
+        def decode():
+            qkv = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda").to(bf)
+            k, v = (torch.randn(B * pages, nkv, ps, hd, device="cuda").to(bf) for _ in range(2))
+            o = torch.empty(B, nh * hd, dtype=bf, device="cuda")
+            ns = ops.decode_splits(B, nh, ctx_len)
+            scratch = torch.empty(max(1, ops.decode_scratch_floats(B, nh, hd, ns)), device="cuda")
+            counters = torch.zeros(B * nh, dtype=torch.int32, device="cuda")
+            return lambda: ops.paged_decode_bf16(qkv, nh * hd, (nh + nkv) * hd, k, v, btB, row_seq, posB, slot_map, o, scratch,
+                                                 counters, nh, nkv, hd, ps, hd ** -0.5, 0, ns, **extra)
+        timed(decode, B * ctx_len * 2 * nkv * hd * 2, name)
     return out
 
 
