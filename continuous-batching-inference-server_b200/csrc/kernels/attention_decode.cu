@@ -243,12 +243,12 @@ paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, _
                        const int* block_table, int max_blocks, const int* row_seq, const int* positions,
                        const int* slot_mapping, __nv_bfloat16* __restrict__ out, int out_ld, float* part,
                        unsigned int* counters, int n_head, int n_kv_head, int ps, float scale, int window,
-                       int nsplit) {
+                       int nsplit, const float* __restrict__ sinks) {
   __shared__ DecodeTcShared<HD> sm;
   pdl_trigger();
   decode_tc_item<HD, true, (HD <= 64 ? 2 : 1)>(qkv, ld, k_off, v_off, kc, vc, block_table, max_blocks, row_seq, positions, slot_mapping, out,
                            out_ld, part, counters, n_head, n_kv_head, ps, scale, window, nsplit, blockIdx.x, blockIdx.y,
-                           blockIdx.z, threadIdx.x, sm, 0);
+                           blockIdx.z, threadIdx.x, sm, 0, sinks);
 }
 
 // After a decode step whose next tokens were chosen on the device: the chosen token becomes the
@@ -305,10 +305,11 @@ CBIS_EXPORT int cbis_paged_decode_bf16(const void* qkv, int ld, int k_off, int v
                                        int v_row, const float* slopes, const float* sinks, float temp_coef,
                                        int temp_every) {
   if (rows <= 0) return CBIS_OK;
-  // hdv (0: the keys' width, values in pages of their own): the values' width; with it, a bias, a sink or a
-  // temperature the lane-group form runs whatever the head size
-  const bool extended = hdv > 0 || slopes || sinks || temp_every > 0;
+  // hdv (0: the keys' width, values in pages of their own): the values' width.  With values of another width or in
+  // the keys' rows, a bias or a temperature the lane-group form runs whatever the head size; a sink alone is
+  // taken by both forms (it joins the denominator where the parts are merged)
   if (hdv <= 0) hdv = hd, v_row = hd;
+  const bool extended = hdv != hd || v_row != hd || slopes || temp_every > 0;
   if (hdv > 256 || hdv % 8 || v_row < hdv || v_row % 8) return CBIS_ERR_BAD_SIZE;
   if (hd <= 0 || hd > 256 || hd % 8 || ps <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head || nsplit < 1 || nsplit > 32)
     return CBIS_ERR_BAD_SIZE;
@@ -325,12 +326,12 @@ CBIS_EXPORT int cbis_paged_decode_bf16(const void* qkv, int ld, int k_off, int v
       e = launch_pdl(paged_decode_tc_kernel<128>, grid, dim3(DEC_WARPS * 32), 0, st, (const __nv_bfloat16*)qkv, ld, k_off,
                      v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, block_table, max_blocks, row_seq, positions,
                      slot_mapping, (__nv_bfloat16*)out, out_ld, part, counters, n_head, n_kv_head, ps, scale, window,
-                     nsplit);
+                     nsplit, sinks);
     else
       e = launch_pdl(paged_decode_tc_kernel<64>, grid, dim3(DEC_WARPS * 32), 0, st, (const __nv_bfloat16*)qkv, ld, k_off,
                      v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, block_table, max_blocks, row_seq, positions,
                      slot_mapping, (__nv_bfloat16*)out, out_ld, part, counters, n_head, n_kv_head, ps, scale, window,
-                     nsplit);
+                     nsplit, sinks);
     return (int)e;
   }
 #define CBIS_DEC(LPK)                                                                                             \

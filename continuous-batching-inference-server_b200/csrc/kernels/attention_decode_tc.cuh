@@ -83,7 +83,8 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
                                                const int* row_seq, const int* positions, const int* slot_mapping,
                                                __nv_bfloat16* out, int out_ld, float* part, unsigned int* counters,
                                                int n_head, int n_kv_head, int ps, float scale, int window, int nsplit,
-                                               int row, int h, int split, int tid, DecodeTcShared<HD>& sm, int bar) {
+                                               int row, int h, int split, int tid, DecodeTcShared<HD>& sm, int bar,
+                                               const float* __restrict__ sinks = nullptr) {
   constexpr int NC = HD / 32;        // 16-byte loads per key for the score fragments (4 lanes x 16 B = 32 dims each)
   constexpr int LPK = HD / 8;        // lanes per key in the coalesced V loads
   constexpr int KPL = 32 / LPK;      // keys per warp-wide V load
@@ -276,12 +277,19 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
     wgt[w] = sm.m[w] > -INFINITY ? expf(sm.m[w] - M) : 0.f;
     L += sm.l[w] * wgt[w];
   }
+  // a sink (one number per head) joins the denominator only: with the larger of the two as the reference
+  float keep1 = 1.f;
+  if (sinks && nsplit == 1) {
+    const float sk = sinks[h], mm = fmaxf(M, sk);
+    keep1 = expf(M - mm);
+    L = fmaf(L, keep1, expf(sk - mm));
+  }
   for (int tt = tid; tt < HD; tt += NT) {
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w) v += sm.acc[w][tt] * wgt[w];
     if (nsplit == 1) {
-      out[(size_t)row * out_ld + h * HD + tt] = __float2bfloat16_rn(v / L);
+      out[(size_t)row * out_ld + h * HD + tt] = __float2bfloat16_rn(v * keep1 / L);
     } else {
       float* p = part + (((size_t)row * n_head + h) * nsplit + split) * (HD + 2);
       p[tt] = v;
@@ -303,10 +311,11 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
   if (warp == 0) {
     const float ms = lane < nsplit ? __ldcg(p + (size_t)lane * (HD + 2) + HD) : -INFINITY;
     const float ls = lane < nsplit ? __ldcg(p + (size_t)lane * (HD + 2) + HD + 1) : 0.f;
-    const float Mx = warp_max(ms);
+    const float sk = sinks ? sinks[h] : -INFINITY;
+    const float Mx = fmaxf(warp_max(ms), sk);
     const float w = ms > -INFINITY ? expf(ms - Mx) : 0.f;
     sm.w[lane] = w;
-    const float Ls = warp_sum(ls * w);
+    const float Ls = warp_sum(ls * w) + (sinks ? expf(sk - Mx) : 0.f);
     if (lane == 0) sm.inv = 1.f / Ls;
   }
   group_sync(bar, NT);

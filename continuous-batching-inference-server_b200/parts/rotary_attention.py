@@ -52,9 +52,8 @@ class RotaryAttention(Mixer):
         self.rot_stretch = None if rot_stretch is None else tuple(float(v) for v in rot_stretch)
         self.unit_sink, self.value_blend = bool(unit_sink), value_blend
         self.d_q, self.d_kv, self.d_v = self.n_head * self.head_dim, self.n_kv_head * self.head_dim, self.n_kv_head * self.v_head_dim
-        if self.d_q + self.d_kv > ops.QK_PREPARE_MAX_WIDTH:
-            raise ValueError(f"queries and keys of a token are {self.d_q + self.d_kv} entries together; the kernel that "
-                             f"prepares them takes up to {ops.QK_PREPARE_MAX_WIDTH}")
+        # wider rows than the kernel that prepares q and k in one pass holds: the same in kernels of their own
+        self.one_pass = self.d_q + self.d_kv <= ops.QK_PREPARE_MAX_WIDTH
         self.names = tuple(names)
         self.w_in = self.w_out = self.q_norm_w = self.k_norm_w = self.freqs = self.sinks = None
         self.blend = 0.0
@@ -103,7 +102,7 @@ class RotaryAttention(Mixer):
             if other is None or other.shape != (T, self.d_v):
                 raise RuntimeError("a layer that blends its values needs an earlier layer of the step that left values "
                                    f"of the same shape [{T}, {self.d_v}]")
-        if ops.USE_QK_PREPARE:
+        if ops.USE_QK_PREPARE and self.one_pass:
             if self.qk_norm or self.rot_dims or other is not None:
                 ops.qk_prepare(proj, 0, self.n_head, k0, self.n_kv_head, self.head_dim, self.q_norm_w, self.k_norm_w,
                                self.eps, ctx.positions, self.freqs, self.rot_dims, v0, self.d_v, other, self.blend)

@@ -209,6 +209,46 @@ def test_attention_kernels_with_a_sink_of_score_zero(dtype):
                 assert (out3.double().cpu() - ref[last]).abs().max() < tol, (D, V, "decode", nsplit)
 
 
+def test_decode_kernel_tensor_core_form_with_a_sink():
+    """Head sizes 64 and 128 with values as wide as the keys on pages of 16 and 32 keys: the decode kernel's
+    tensor-core form takes the 1 in the denominator, with the keys of a row in one part and split over several
+    blocks; rows at the first positions (where the 1 holds most of the denominator), at a page's last key and its
+    first, and far into the context."""
+    from cbis_b200.kernels import ops
+    g = torch.Generator().manual_seed(15)
+    H, G = 4, 2
+    for D, ps in ((64, 16), (128, 16), (64, 32)):
+        n = 300
+        q = rounded(torch.randn(n, H * D, generator=g), "bfloat16")
+        k = rounded(torch.randn(n, G, D, generator=g), "bfloat16")
+        v = rounded(torch.randn(n, G, D, generator=g), "bfloat16")
+        scale = 0.3 / D ** 0.5
+        pages = -(-n // ps)
+        perm = torch.randperm(pages, generator=g)
+        kp, vp = torch.zeros(pages, G, ps, D), torch.zeros(pages, G, ps, D)
+        for p in range(n):
+            kp[perm[p // ps], :, p % ps] = k[p].float()
+            vp[perm[p // ps], :, p % ps] = v[p].float()
+        ref = torch.from_numpy(pv.attention_rows(q.view(n, H, D).numpy(), k.numpy(), v.numpy(), scale)).view(n, H * D)
+        rows = torch.tensor([0, 1, ps - 1, ps, 2 * ps, 127, 128, 255, 256, n - 1])
+        qd = dev(q[rows].float(), "bfloat16")
+        pos = rows.int().cuda()
+        seq = torch.zeros(len(rows), dtype=torch.int32, device="cuda")
+        bt = perm.int().view(1, pages).cuda()
+        sk = torch.zeros(H, device="cuda")
+        for nsplit in (1, 3):
+            out = torch.zeros(len(rows), H * D, dtype=torch.bfloat16, device="cuda")
+            scratch = torch.empty(max(1, ops.decode_scratch_floats(len(rows), H, D, nsplit)), device="cuda")
+            counters = torch.zeros(len(rows) * H, dtype=torch.int32, device="cuda")
+            ops.paged_decode_bf16(qd, -1, -1, dev(kp, "bfloat16"), dev(vp, "bfloat16"), bt, seq, pos, pos, out, scratch, counters,
+                                  H, G, D, ps, scale, 0, nsplit, v_head_dim=D, sinks=sk)
+            assert (out.double().cpu() - ref[rows]).abs().max() < 2e-2, (D, ps, nsplit)
+            plain = torch.zeros_like(out)              # without the sink the first rows differ by far more
+            ops.paged_decode_bf16(qd, -1, -1, dev(kp, "bfloat16"), dev(vp, "bfloat16"), bt, seq, pos, pos, plain, scratch, counters,
+                                  H, G, D, ps, scale, 0, nsplit)
+            assert (plain.double().cpu() - ref[rows])[:2].abs().max() > 0.2, (D, ps, nsplit)
+
+
 # ---- each mechanism as a model of one layer, and the mixed models -------------------------------------------
 ONE_LAYER = {
     "retention": config(48, 50, [ret(2, 16, 8, [0.95, 0.999], base=40.0, rot_dims=12, mlp=dense(32))]),
