@@ -21,7 +21,7 @@ class RotaryAttention(Mixer):
       i + rot_dims/2, angle p * rot_base^(-2i/rot_dims), optionally stretched: ``rotary_frequencies``).  Keys are
       cached rotated.
     * ``unit_sink``: the softmax's denominator holds 1 more than the sum over the keys, p_j = exp(s_j) / (1 + sum
-      exp(s)): a sink of score 0 that has no value.
+      exp(s)): the weights of the keys sum to less than one, what is missing goes nowhere.
     * ``value_blend``: "source": this layer's values, as projected, are left for the later layers of the step;
       "blend": v <- (1 - lambda) v + lambda v_source with the source layer's values of the same token and lambda
       the layer's own scalar ``<blend>``; the blended values are what is cached.  None: neither.
