@@ -919,26 +919,58 @@ QK_PREPARE_MAX_WIDTH = 200 * 1024 // 4 - 64              # q and k of a row toge
 USE_QK_PREPARE = __import__("os").environ.get("CBIS_QK_PREPARE", "1") != "0"   # 0: norm, rotation and blending before attention run as kernels of their own
 
 
+# A long segment of a retention layer is cut into pieces that run side by side where the step's blocks are few (one
+# prompt offers heads x columns / 16 of them, and its rows wait on one another): see ``retention``.
+RETENTION_PIECE_ROWS = 128            # rows of a piece (a multiple of the kernel's batches of 32 rows)
+RETENTION_PIECES_FROM = 384           # the longest segment of a step from which segments are cut
+RETENTION_PIECES_MAX_BLOCKS = 1184    # blocks of the uncut step (segments x heads x columns / 16) up to which they are: 8 a SM
+RETENTION_PIECES_MAX_BYTES = 1 << 29  # the most scratch (start states of all pieces) a step may take
+
+
 def retention(qkv, q_off, k_off, v_off, positions, freqs, rot_dims, k_scale, one_minus_decay, state, seg_slot, cu_rows,
-              n_segments, heads, dim, v_dim, y, max_seg_rows: int = 0):
+              n_segments, heads, dim, v_dim, y, max_seg_rows: int = 0, decay_piece=None, piece_rows=None):
     """Retention over every segment's rows, from and into the requests' states: per head S <- decay S + k v^T,
     y = S^T q, after the first ``rot_dims`` entries of q and k were rotated in pairs (entry i with i + rot_dims/2) by
     position * freqs[i] and k was multiplied by ``k_scale``.  ``qkv``: the compute type, q | k | v at their column
     offsets; ``one_minus_decay``: 32-bit ``[heads]``, 1 - decay per head; ``y``: 32-bit ``[T, heads * v_dim]``;
-    ``state``: 32-bit ``[slots, heads * v_dim * dim]``; ``max_seg_rows``: the step's longest segment if known."""
-    _need_cuda(qkv, positions, freqs, one_minus_decay, state, seg_slot, cu_rows, y)
+    ``state``: 32-bit ``[slots, heads * v_dim * dim]``; ``max_seg_rows``: the step's longest segment if known.
+
+    A segment's rows are walked in order.  With ``decay_piece`` (32-bit ``[heads]``: decay^piece_rows, ``piece_rows``
+    defaulting to ``RETENTION_PIECE_ROWS``), where the step's longest segment is long and its blocks are few, segments
+    are cut into pieces that run side by side: every piece's end state from zero, then the start states one after the
+    other (start[p + 1] = decay^piece_rows start[p] + end[p]), then every piece again from its start state.  That is
+    twice the arithmetic for many times the parallel work; against the walk in one piece the results differ by
+    rounding only.  ``piece_rows=0``: never cut."""
+    _need_cuda(qkv, positions, freqs, one_minus_decay, state, seg_slot, cu_rows, y, decay_piece)
     T = qkv.shape[0]
     assert qkv.stride(1) == 1 and positions.dtype == torch.int32 and positions.shape[0] >= T
     assert y.dtype == torch.float32 and y.stride(1) == 1 and y.shape == (T, heads * v_dim)
     assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= heads * v_dim * dim
     assert one_minus_decay.dtype == torch.float32 and one_minus_decay.numel() == heads and one_minus_decay.is_contiguous()
     assert rot_dims == 0 or (freqs.dtype == torch.float32 and freqs.numel() >= rot_dims // 2 and freqs.is_contiguous())
+    longest = int(max_seg_rows or 0)
+    n_pieces, starts = 1, None
+    if decay_piece is not None and piece_rows != 0:
+        assert decay_piece.dtype == torch.float32 and decay_piece.numel() == heads and decay_piece.is_contiguous()
+        explicit = piece_rows is not None
+        piece_rows = int(piece_rows) if explicit else RETENTION_PIECE_ROWS
+        assert piece_rows > 0 and piece_rows % 32 == 0
+        n = -(-longest // piece_rows)
+        per_state = heads * v_dim * dim
+        if n > 1 and (explicit or (longest >= RETENTION_PIECES_FROM
+                                   and n_segments * heads * -(-v_dim // 16) <= RETENTION_PIECES_MAX_BLOCKS
+                                   and n_segments * n * per_state * 4 <= RETENTION_PIECES_MAX_BYTES
+                                   and n_segments * n <= 65535)):
+            n_pieces = n
+            starts = torch.empty((n_segments * n_pieces, per_state), dtype=torch.float32, device=qkv.device)
     st = kernels().cbis_retention(_ptr(qkv), c_int(qkv.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), _ptr(positions),
                                   _ptr(freqs), c_int(rot_dims), c_float(k_scale), _ptr(one_minus_decay), _ptr(state),
                                   ctypes.c_longlong(state.stride(0)), _ptr(seg_slot), _ptr(cu_rows), _ptr(y),
                                   c_int(y.stride(0)), c_int(n_segments), c_int(heads), c_int(dim), c_int(v_dim),
-                                  c_int(dtype_code(qkv.dtype)), _stream(), c_int(int(max_seg_rows)))
-    _check(st, "retention", f"segments={n_segments} heads={heads} dim={dim} v_dim={v_dim} rot_dims={rot_dims}")
+                                  c_int(dtype_code(qkv.dtype)), _stream(), c_int(longest), c_int(n_pieces),
+                                  c_int(piece_rows or 0), _ptr(starts), _ptr(decay_piece if n_pieces > 1 else None))
+    _check(st, "retention", f"segments={n_segments} heads={heads} dim={dim} v_dim={v_dim} rot_dims={rot_dims} "
+                            f"pieces={n_pieces}", launches=3 if n_pieces > 1 else 1)
 
 
 def qk_prepare(buf, q_off, q_heads, k_off, k_heads, width, q_weight, k_weight, eps, positions, freqs, rot_dims,

@@ -22,7 +22,8 @@ class RetentionMixer(Mixer):
 
     Per request the mixer keeps S (zero at the start), 32-bit; a step walks each segment's rows in order from that
     state, so prompt portions cut anywhere, single decoded tokens and whole prompts give the same values.  Nothing is
-    cached per token.  q | k | v | gate are one product; rotation and scale happen inside the recurrence kernel, on
+    cached per token.  Long segments of a step with little parallel work are cut into pieces that run side by side
+    (``ops.retention``; the results differ from the walk in one piece by rounding only).  q | k | v | gate are one product; rotation and scale happen inside the recurrence kernel, on
     32-bit values.  ``names``: what follows the layer's prefix in the tensors' names (q, k, v, the gate, the output
     matrix)."""
 
@@ -45,7 +46,7 @@ class RetentionMixer(Mixer):
         self.k_scale = float(k_scale) if k_scale is not None else self.dim ** -0.5
         self.d_qk, self.d_v = self.heads * self.dim, self.heads * self.v_dim
         self.names = tuple(names)
-        self.w_in = self.w_out = self.freqs = self.one_minus_decay = None
+        self.w_in = self.w_out = self.freqs = self.one_minus_decay = self.decay_piece = None
 
     def state_need(self):
         return StateNeed((self.heads * self.v_dim * self.dim,), torch.float32)
@@ -63,6 +64,9 @@ class RetentionMixer(Mixer):
         self.freqs = rotary_frequencies(self.rot_base, self.rot_dims, self.rot_stretch).to(device)
         # 1 - decay in 64-bit, rounded once: a decay near 1 keeps its digits
         self.one_minus_decay = torch.tensor([1.0 - d for d in self.decays], dtype=torch.float64).to(torch.float32).to(device)
+        # what a whole piece of a cut segment takes off a state, in 64-bit, rounded once
+        self.decay_piece = torch.tensor([d ** ops.RETENTION_PIECE_ROWS for d in self.decays],
+                                        dtype=torch.float64).to(torch.float32).to(device)
 
     def streamed_weights(self):
         return [self.w_in, self.w_out]
@@ -73,7 +77,7 @@ class RetentionMixer(Mixer):
         y = torch.empty((T, self.d_v), dtype=torch.float32, device=h.device)
         ops.retention(proj, 0, self.d_qk, 2 * self.d_qk, ctx.positions, self.freqs, self.rot_dims, self.k_scale,
                       self.one_minus_decay, state, ctx.seg_slot, ctx.cu_rows, ctx.n_segments, self.heads, self.dim,
-                      self.v_dim, y, max_seg_rows=ctx.max_seg_rows)
+                      self.v_dim, y, max_seg_rows=ctx.max_seg_rows, decay_piece=self.decay_piece)
         g = torch.empty((T, self.d_v), dtype=h.dtype, device=h.device)
         g0 = 2 * self.d_qk + self.d_v
         ops.rms_norm(y, None, self.eps, g, parts=self.heads, gate=proj[:, g0:g0 + self.d_v], gate_act=self.gate_act,

@@ -104,6 +104,70 @@ def test_retention_recurrence_over_steps(H, D, V, dims, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H, D, V, dims, piece", [(3, 16, 24, 16, 32), (2, 48, 40, 24, 64), (1, 300, 20, 0, 32), (3, 64, 64, 64, 128)])
+def test_long_segments_cut_into_pieces_that_run_side_by_side(H, D, V, dims, piece, dtype):
+    """Segments longer than a piece, as long as one, a multiple of it, one row more and one row fewer, and a short
+    one, from states that earlier rows left: the pieces' end states from zero, the start states one after the other
+    and the second walk give what the walk in one piece gives, and leave the same state (a decay of 1 among them)."""
+    from cbis_b200.kernels import ops
+    g = torch.Generator().manual_seed(9)
+    before = [5, 0, 40, 1, 0, 7]
+    lens = [4 * piece + 9, piece, 3 * piece, 2 * piece + 1, 2 * piece - 1, 3]
+    n_req = len(lens)
+    decays = [1.0, 0.96875, 0.99951171875][:H] if H > 1 else [0.9901568667976963]
+    freqs = pv.frequencies(10000.0, dims) if dims else np.zeros(0)
+    ks = D ** -0.5
+    fd = torch.tensor(freqs, dtype=torch.float64).float().cuda()
+    om = torch.tensor([1.0 - d for d in decays], dtype=torch.float64).float().cuda()
+    dp = torch.tensor([d ** piece for d in decays], dtype=torch.float64).float().cuda()
+    rows = [b + n for b, n in zip(before, lens)]
+    qkv = [rounded(torch.randn(r, 2 * H * D + H * V, generator=g), dtype) for r in rows]
+    refs, ends = [], []
+    for x, r in zip(qkv, rows):
+        pos = np.arange(r)
+        q, k = x[:, :H * D].view(r, H, D).numpy(), x[:, H * D:2 * H * D].view(r, H, D).numpy()
+        v = x[:, 2 * H * D:].view(r, H, V).numpy()
+        if dims:
+            q, k = pv.rotate(q, pos, freqs, dims), pv.rotate(k, pos, freqs, dims)
+        o, S = pv.retention_rows(q, k * ks, v, decays)
+        refs.append(torch.from_numpy(o).view(r, H * V))
+        ends.append(S)
+
+    def run(piece_rows):
+        state = torch.zeros(n_req, H * V * D, device="cuda")
+        out = []
+        for part in (0, 1):                       # the rows before, then the long segments, all requests in one step
+            segs = [(x[:b] if part == 0 else x[b:]) for x, b in zip(qkv, before)]
+            live = [i for i, s in enumerate(segs) if s.shape[0]]
+            cu = np.cumsum([0] + [segs[i].shape[0] for i in live])
+            pos = np.concatenate([np.arange(segs[i].shape[0]) + (before[i] if part else 0) for i in live])
+            y = torch.empty(int(cu[-1]), H * V, dtype=torch.float32, device="cuda")
+            ops.retention(dev(torch.cat([segs[i] for i in live]).float(), dtype), 0, H * D, 2 * H * D,
+                          torch.tensor(pos, dtype=torch.int32, device="cuda"), fd, dims, ks, om, state,
+                          torch.tensor(live, dtype=torch.int32, device="cuda"), torch.tensor(cu, dtype=torch.int32, device="cuda"),
+                          len(live), H, D, V, y, max_seg_rows=max(segs[i].shape[0] for i in live),
+                          decay_piece=dp if part else None, piece_rows=piece_rows if part else 0)
+            out.append((live, cu, y.double().cpu()))
+        return out[1], state.double().cpu()
+
+    (live, cu, y_cut), s_cut = run(piece)
+    (_, _, y_one), s_one = run(0)
+    tol = 2e-4 if dims else 2e-5
+    for j, i in enumerate(live):
+        ref = refs[i][before[i]:]
+        scale = max(1.0, ref.abs().max().item())
+        assert (y_one[cu[j]:cu[j + 1]] - ref).abs().max() < tol * scale
+        assert (y_cut[cu[j]:cu[j + 1]] - ref).abs().max() < tol * scale
+        assert (y_cut[cu[j]:cu[j + 1]] - y_one[cu[j]:cu[j + 1]]).abs().max() < 2e-5 * scale      # rounding only
+        S = torch.from_numpy(np.ascontiguousarray(np.asarray(ends[i]).transpose(0, 2, 1))).reshape(-1)   # kept as [H][V][D]
+        s_scale = max(1.0, S.abs().max().item())
+        assert (s_cut[i] - S).abs().max() < tol * s_scale
+        assert (s_cut[i] - s_one[i]).abs().max() < 2e-5 * s_scale
+    short = live.index(5)                          # a segment inside one piece walks its rows once: the same bits
+    assert torch.equal(y_cut[cu[short]:cu[short + 1]], y_one[cu[short]:cu[short + 1]])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_queries_and_keys_prepared_in_one_pass(dtype):
     """One norm over all of q and one over all of k, the rotation of every head, blended values: the one-pass kernel
     against the plain functions, and against the same steps as kernels of their own."""
