@@ -501,6 +501,31 @@ def test_far_tokens_held_by_a_slow_decay_and_long_decoding():
                 assert err.max() < tol and err.median() < tol / 4, (sizes, err.max().item(), err.median().item())
 
 
+def test_a_long_prompt_whose_retention_runs_in_pieces():
+    """A prompt long enough that the engine cuts its retention segments into pieces: whole, in two long portions (the
+    second from the state the first left), after a short portion, and in portions too short to be cut, all give the
+    plain implementation's logits; one head never forgets, one forgets within a piece."""
+    from cbis_b200.kernels import ops
+    n = ops.RETENTION_PIECES_FROM + 3 * ops.RETENTION_PIECE_ROWS + 37
+    cfgd = config(48, 50, [ret(3, 16, 24, [1.0, 0.96875, 0.9990234375], base=1000.0, mlp=dense(32)),
+                           attn(2, 1, 16, 16, 0.25, mlp=None),
+                           ret(2, 24, 16, [0.99951171875, 0.9], rot_dims=8, mlp=dense(24))])
+    w = make_weights(cfgd, 21)
+    toks = tokens_of(cfgd, n, 6)
+    ref = plain(cfgd, w, toks)
+    half = ops.RETENTION_PIECES_FROM + ops.RETENTION_PIECE_ROWS + 1
+    for dtype in ("float32", "bfloat16"):
+        eng = make_engine(cfgd, w, dtype, page_size=16, num_pages=-(-n // 16) + 4, max_batched_tokens=n + 8)
+        for sizes in ([n], [half, n - half], [5, n - 5], [200, 200, 200, n - 600]):
+            got = run_cut(eng, toks, sizes)
+            err = (got - ref).abs().max(1).values
+            if dtype == "float32":
+                assert err.max() < 3e-4, (sizes, err.max().item())
+            else:
+                tol = tolerance(dtype, ref)
+                assert err.max() < tol and err.median() < tol / 4, (sizes, err.max().item(), err.median().item())
+
+
 # ---- generation through the scheduler --------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_scheduler(dtype):
