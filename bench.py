@@ -730,9 +730,9 @@ def vatevik_kernels(torch, ops, pk):
             om = torch.tensor([2.0 ** (-5 - h) for h in range(H)], device="cuda")
             st = torch.zeros(segs, H * D * V, device="cuda")
             y = torch.empty(rows, H * V, device="cuda")
-            dp = (1.0 - om.double()).pow(ops.RETENTION_PIECE_ROWS).float()
+            dp = ops.retention_piece_decays((1.0 - om.double()).tolist()).cuda()
             return lambda: ops.retention(qkv, 0, H * D, 2 * H * D, pos, freqs, D, D ** -0.5, om, st, seg_slot, cu, segs, H, D, V, y,
-                                         max_seg_rows=per, decay_piece=dp, piece_rows=None if pieces else 0)
+                                         max_seg_rows=per, piece_decays=dp, piece_rows=None if pieces else 0)
         for pieces in ((True, False) if segs == 1 else (True,)):        # as the engine calls it; the long segment walked in one piece
             timed(retention, rows * ((2 * H * D + H * V) * 2 + H * V * 4) + 2 * segs * H * D * V * 4,
                   f"retention_{tag}" if pieces else f"retention_in_one_piece_{tag}")

@@ -9,11 +9,15 @@
 // a decay near 1 that the rounded decay itself has lost.  A segment's rows are walked in order from the request's
 // state, so a position's values are the same bits whether its prompt came whole, in portions or token by token.
 //
-// grid (column blocks, heads, segments).  A block owns CB columns of S (16, or 32 in steps of short segments); a
-// column is spread over L lanes, lane l holding the rows d = l, l + L, ... in registers.  Rows come through shared
-// memory TC at a time (32; 4 in steps of short segments): k and q as 32-bit (rotated there, one sine and cosine
-// per pair serving both), and the block's slice of v; the next TC rows are on their way from memory, into registers,
-// while these are walked.  State of a slot: S as [H][V][D].
+// grid (column blocks, heads, segments).  A block owns CB columns of S; a thread holds CPT of them (4, 2 where a
+// column is long, 1 in steps of short segments), each spread over L lanes: lane l holds the rows d = l, l + L, ... of
+// its columns in registers, so one key or query entry read from shared memory serves CPT columns.  Rows come through
+// shared memory TC at a time (16; 4 in steps of short segments): k and q as 32-bit (rotated there, one sine and
+// cosine per pair serving both), a lane's entries side by side (16-byte loads, the lanes' runs padded apart so that
+// they meet no bank twice), and the block's slice of v; the next TC rows are on their way from memory, into
+// registers, while these are walked.  A column's L partial sums are added in a tree of shuffles whose first steps
+// halve the columns a lane still carries, so CPT columns take log2(L) + CPT - 2 shuffles and every form adds in the
+// same order.  State of a slot: S as [H][V][D].
 //
 // One long prompt offers heads x columns of parallel work only, and its rows wait on one another.  Where a step's
 // states are few and its longest segment is long, segments are cut into pieces of `piece_rows` rows that run side by
@@ -26,25 +30,30 @@
 
 namespace cbis {
 
-constexpr int kRetRows = 32;      // rows of a batch for long segments
+constexpr int kRetRows = 16;      // rows of a batch for long segments
 constexpr int kRetRowsShort = 4;  // rows of a batch where no segment of the step is longer (decode steps)
 
 __host__ __device__ inline int ret_lanes(int D) { return D <= 256 ? 8 : 16; }
+// floats between the runs of two lanes in a staged row: a multiple of 4 whose quarter is odd
+__host__ __device__ constexpr int ret_run(int npl) { return ((npl + 3) / 4) % 2 ? (npl + 3) / 4 * 4 : (npl + 3) / 4 * 4 + 4; }
 
 enum { kRetWhole = 0, kRetEnds = 1, kRetFromStarts = 2 };
 
-template <typename TT, int NPL, int L, int CB, int TC, int MODE>
-__global__ void __launch_bounds__(CB * L)
+template <typename TT, int NPL, int L, int CPT, int CB, int TC, int MODE>
+__global__ void __launch_bounds__(CB / CPT * L)
 retention_kernel(const TT* qkv, int ld, int q_off, int k_off, int v_off, const int* positions,
                  const float* __restrict__ freqs, int rot_dims, float k_scale, const float* __restrict__ one_minus_decay,
                  float* state, long long slot_stride, const int* seg_slot, const int* cu_rows, float* y, int y_ld, int H,
                  int D, int V, int n_pieces, int piece_rows, float* starts) {
-  constexpr int DP = NPL * L, THREADS = CB * L;
+  static_assert(CPT == 1 || CPT == 2 || CPT == 4, "columns a thread");
+  // a thread of one column reads its entries one by one, a stride of L apart: the rows are staged as they are
+  constexpr bool kRuns = CPT > 1;
+  constexpr int DP = NPL * L, RUN = kRuns ? ret_run(NPL) : NPL, DPP = RUN * L, THREADS = CB / CPT * L;
   constexpr int KQ_PER = (TC * DP + THREADS - 1) / THREADS, V_PER = (TC * CB + THREADS - 1) / THREADS;
-  extern __shared__ float smem[];
-  float* ks = smem;                      // [TC][DP]
-  float* qs = ks + TC * DP;              // [TC][DP]
-  float* vs = qs + TC * DP;              // [TC][CB]
+  extern __shared__ __align__(16) float smem[];
+  float* ks = smem;                      // [TC][L][RUN]: entry d at (d % L) * RUN + d / L (one column a thread: at d)
+  float* qs = ks + TC * DPP;             // the same
+  float* vs = qs + TC * DPP;             // [TC][CB]
   float* nums = vs + TC * CB;            // [TC][CB]
   float* pos = nums + TC * CB;           // [TC]
   pdl_trigger();
@@ -67,25 +76,28 @@ retention_kernel(const TT* qkv, int ld, int q_off, int k_off, int v_off, const i
   }
   if (n_rows <= 0) return;
   const int tid = threadIdx.x;
-  const int l = tid % L, c = tid / L;
-  const int col = xb * CB + c;
-  const bool live = col < V;
-  const size_t at = ((size_t)h * V + (live ? col : 0)) * D;       // the column's place in a state
+  const int l = tid % L, g = tid / L;
+  const int col = xb * CB + g * CPT;           // the first of this thread's columns
+  const size_t at = ((size_t)h * V + (col < V ? col : 0)) * D;       // its place in a state
   float* sp = state + (long long)seg_slot[s] * slot_stride + at;
   const size_t per_state = (size_t)H * V * D;
   const float* from = MODE == kRetFromStarts ? starts + ((size_t)s * n_pieces + piece) * per_state + at : sp;
   float* into = MODE == kRetEnds ? starts + ((size_t)s * n_pieces + piece + 1) * per_state + at : sp;
-  float S[NPL];
+  float S[CPT][NPL];
 #pragma unroll
-  for (int i = 0; i < NPL; ++i) {
-    const int d = l + L * i;
-    S[i] = (MODE != kRetEnds && live && d < D) ? from[d] : 0.f;
+  for (int j = 0; j < CPT; ++j) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int d = l + L * i;
+      S[j][i] = (MODE != kRetEnds && col + j < V && d < D) ? from[(size_t)j * D + d] : 0.f;
+    }
   }
   const TT* qrow = qkv + (size_t)row0 * ld + q_off + h * D;
   const TT* krow = qkv + (size_t)row0 * ld + k_off + h * D;
   const TT* vrow = qkv + (size_t)row0 * ld + v_off + h * V + xb * CB;
   const int vcols = min(CB, V - xb * CB);
   const int half = rot_dims / 2;
+  auto staged = [](int d) { return kRuns ? (d % L) * RUN + d / L : d; };
 
   // what this thread fetches of a batch of rows: entries of k and q (row t = idx / DP, entry d = idx % DP), of the
   // block's slice of v, and (the first TC threads) a row's position
@@ -114,8 +126,9 @@ retention_kernel(const TT* qkv, int ld, int q_off, int k_off, int v_off, const i
     for (int j = 0; j < KQ_PER; ++j) {
       const int idx = tid + THREADS * j;
       if (idx < TC * DP) {
-        ks[idx] = r_k[j] * k_scale;      // a rotation is linear: the key's scale may come first
-        if (MODE != kRetEnds) qs[idx] = r_q[j];
+        const int at_s = (idx / DP) * DPP + staged(idx % DP);
+        ks[at_s] = r_k[j] * k_scale;      // a rotation is linear: the key's scale may come first
+        if (MODE != kRetEnds) qs[at_s] = r_q[j];
       }
     }
 #pragma unroll
@@ -131,44 +144,95 @@ retention_kernel(const TT* qkv, int ld, int q_off, int k_off, int v_off, const i
       const int t = u / half, i = u % half;
       float sn, cs;
       sincosf(pos[t] * freqs[i], &sn, &cs);
-      float* kt = ks + t * DP;
-      float* qt = qs + t * DP;
-      const float ka = kt[i], kb = kt[i + half];
-      kt[i] = ka * cs - kb * sn;
-      kt[i + half] = kb * cs + ka * sn;
+      float* kt = ks + t * DPP;
+      float* qt = qs + t * DPP;
+      const int ia = staged(i), ib = staged(i + half);
+      const float ka = kt[ia], kb = kt[ib];
+      kt[ia] = ka * cs - kb * sn;
+      kt[ib] = kb * cs + ka * sn;
       if (MODE != kRetEnds) {
-        const float qa = qt[i], qb = qt[i + half];
-        qt[i] = qa * cs - qb * sn;
-        qt[i + half] = qb * cs + qa * sn;
+        const float qa = qt[ia], qb = qt[ib];
+        qt[ia] = qa * cs - qb * sn;
+        qt[ib] = qb * cs + qa * sn;
       }
     }
     __syncthreads();
-    if constexpr (MODE == kRetEnds) {          // the end state only: no y
-#pragma unroll 4
-      for (int t = 0; t < tc; ++t) {
-        const float vv = vs[t * CB + c];
-        const float* kt = ks + t * DP + l;
+#pragma unroll 2
+    for (int t = 0; t < tc; ++t) {
+      float kk[(NPL + 3) / 4 * 4], qq[(NPL + 3) / 4 * 4], vv[CPT];
+      if constexpr (kRuns) {
+        const float4* k4 = reinterpret_cast<const float4*>(ks + t * DPP + l * RUN);
+        const float4* q4 = reinterpret_cast<const float4*>(qs + t * DPP + l * RUN);
 #pragma unroll
-        for (int i = 0; i < NPL; ++i) S[i] = fmaf(vv, kt[L * i], fmaf(-om, S[i], S[i]));
-      }
-    } else {
-#pragma unroll 4
-      for (int t = 0; t < tc; ++t) {
-        const float vv = vs[t * CB + c];
-        const float* kt = ks + t * DP + l;
-        const float* qt = qs + t * DP + l;
-        float a0 = 0.f, a1 = 0.f;
+        for (int i = 0; i < (NPL + 3) / 4; ++i) {
+          const float4 a = k4[i];
+          kk[4 * i] = a.x, kk[4 * i + 1] = a.y, kk[4 * i + 2] = a.z, kk[4 * i + 3] = a.w;
+          if (MODE != kRetEnds) {
+            const float4 b = q4[i];
+            qq[4 * i] = b.x, qq[4 * i + 1] = b.y, qq[4 * i + 2] = b.z, qq[4 * i + 3] = b.w;
+          }
+        }
+      } else {
 #pragma unroll
         for (int i = 0; i < NPL; ++i) {
-          S[i] = fmaf(vv, kt[L * i], fmaf(-om, S[i], S[i]));
-          if (i & 1) a1 = fmaf(S[i], qt[L * i], a1);
-          else a0 = fmaf(S[i], qt[L * i], a0);
+          kk[i] = ks[t * DPP + l + L * i];
+          if (MODE != kRetEnds) qq[i] = qs[t * DPP + l + L * i];
         }
-        float acc = a0 + a1;
-#pragma unroll
-        for (int o = 1; o < L; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (l == 0) nums[t * CB + c] = acc;
       }
+      if constexpr (CPT == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(vs + t * CB + g * 4);
+        vv[0] = a.x, vv[1] = a.y, vv[2] = a.z, vv[3] = a.w;
+      } else if constexpr (CPT == 2) {
+        const float2 a = *reinterpret_cast<const float2*>(vs + t * CB + g * 2);
+        vv[0] = a.x, vv[1] = a.y;
+      } else {
+        vv[0] = vs[t * CB + g];
+      }
+      if constexpr (MODE == kRetEnds) {          // the end state only: no y
+#pragma unroll
+        for (int i = 0; i < NPL; ++i)
+#pragma unroll
+          for (int j = 0; j < CPT; ++j) S[j][i] = fmaf(vv[j], kk[i], fmaf(-om, S[j][i], S[j][i]));
+      } else {
+        float a0[CPT], a1[CPT], acc[CPT];
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) a0[j] = a1[j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+#pragma unroll
+          for (int j = 0; j < CPT; ++j) {
+            S[j][i] = fmaf(vv[j], kk[i], fmaf(-om, S[j][i], S[j][i]));
+            if (i & 1) a1[j] = fmaf(S[j][i], qq[i], a1[j]);
+            else a0[j] = fmaf(S[j][i], qq[i], a0[j]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) acc[j] = a0[j] + a1[j];
+        // the sum over a column's lanes; a lane passes on the columns its partner keeps
+        float sum;
+        int mine = 0, o = 1;                       // the column (of CPT) whose sum this lane ends with
+        if constexpr (CPT == 4) {
+          const bool hi = l & 1, hi2 = l & 2;
+          float k0 = hi ? acc[2] : acc[0], k1 = hi ? acc[3] : acc[1];
+          k0 += __shfl_xor_sync(0xffffffffu, hi ? acc[0] : acc[2], 1);
+          k1 += __shfl_xor_sync(0xffffffffu, hi ? acc[1] : acc[3], 1);
+          sum = (hi2 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, hi2 ? k0 : k1, 2);
+          mine = 2 * (l & 1) + ((l >> 1) & 1);
+          o = 4;
+        } else if constexpr (CPT == 2) {
+          const bool hi = l & 1;
+          sum = (hi ? acc[1] : acc[0]) + __shfl_xor_sync(0xffffffffu, hi ? acc[0] : acc[1], 1);
+          mine = l & 1;
+          o = 2;
+        } else {
+          sum = acc[0];
+        }
+#pragma unroll
+        for (; o < L; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (l < CPT) nums[t * CB + g * CPT + mine] = sum;
+      }
+    }
+    if constexpr (MODE != kRetEnds) {
       __syncthreads();
       for (int i = tid; i < tc * CB; i += THREADS) {
         const int t = i / CB, cc = i % CB;
@@ -176,11 +240,14 @@ retention_kernel(const TT* qkv, int ld, int q_off, int k_off, int v_off, const i
       }
     }
   }
-  if (live && (MODE != kRetFromStarts || last)) {
+  if (MODE != kRetFromStarts || last) {
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      const int d = l + L * i;
-      if (d < D) into[d] = S[i];
+    for (int j = 0; j < CPT; ++j) {
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        const int d = l + L * i;
+        if (col + j < V && d < D) into[(size_t)j * D + d] = S[j][i];
+      }
     }
   }
 }
@@ -221,39 +288,41 @@ static int launch_retention(const void* qkv, int ld, int q_off, int k_off, int v
                             const float* decay_piece, cudaStream_t st) {
   const int L = ret_lanes(D);
   const int npl = (D + L - 1) / L;
-  // long segments: blocks of 16 columns walking 32 rows a batch; steps of short segments (decoding): blocks of 32
-  // columns (half as many blocks fetch k and q) and batches of 4 rows
+  // long segments: 16 threads a lane of 4 columns each (2 where a column takes more than 16 registers a lane),
+  // walking 16 rows a batch; steps of short segments (decoding): blocks of 32 columns, one a thread, and batches of 4
   const bool shorts = max_seg_rows > 0 && max_seg_rows <= kRetRowsShort;
-#define CBIS_RET_AS(NPL, LL, CBB, TCC, MODE, Z)                                                                      \
+#define CBIS_RET_AS(NPL, LL, CPT, TCC, MODE, Z)                                                                      \
   do {                                                                                                               \
-    const size_t smem = ((size_t)2 * TCC * NPL * LL + 2 * TCC * CBB + TCC) * sizeof(float);                          \
+    constexpr int CBB = CPT == 1 ? 32 : 16 * CPT;                                                                    \
+    const size_t smem = ((size_t)2 * TCC * (CPT > 1 ? ret_run(NPL) : NPL) * LL + 2 * TCC * CBB + TCC) * sizeof(float); \
     if (smem > 48 * 1024)                                                                                            \
-      cudaFuncSetAttribute(retention_kernel<TT, NPL, LL, CBB, TCC, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                           (int)smem);                                                                               \
-    err = launch_pdl(retention_kernel<TT, NPL, LL, CBB, TCC, MODE>, dim3((V + CBB - 1) / CBB, H, Z), dim3(CBB * LL), \
-                     smem, st, (const TT*)qkv, ld, q_off, k_off, v_off, positions, freqs, rot_dims, k_scale,         \
-                     one_minus_decay, state, slot_stride, seg_slot, cu_rows, y, y_ld, H, D, V, n_pieces, piece_rows, \
-                     starts);                                                                                        \
+      cudaFuncSetAttribute(retention_kernel<TT, NPL, LL, CPT, CBB, TCC, MODE>,                                       \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                                  \
+    err = launch_pdl(retention_kernel<TT, NPL, LL, CPT, CBB, TCC, MODE>, dim3((V + CBB - 1) / CBB, H, Z),            \
+                     dim3(CBB / CPT * LL), smem, st, (const TT*)qkv, ld, q_off, k_off, v_off, positions, freqs,      \
+                     rot_dims, k_scale, one_minus_decay, state, slot_stride, seg_slot, cu_rows, y, y_ld, H, D, V,    \
+                     n_pieces, piece_rows, starts);                                                                  \
   } while (0)
 #define CBIS_RET(NPL, LL)                                                                                            \
   do {                                                                                                               \
     cudaError_t err = cudaSuccess;                                                                                   \
+    constexpr int CPT = NPL <= 16 ? 4 : 2;                                                                           \
     if (n_pieces > 1) {                                                                                              \
       const int HVD = H * V * D;                                                                                     \
-      CBIS_RET_AS(NPL, LL, 16, kRetRows, kRetEnds, S * n_pieces);                                                    \
+      CBIS_RET_AS(NPL, LL, CPT, kRetRows, kRetEnds, S * n_pieces);                                                   \
       if (err != cudaSuccess) return (int)err;                                                                       \
       err = launch_pdl(retention_starts_kernel, dim3((HVD + 255) / 256, S), dim3(256), 0, st, starts,                \
                        (const float*)state, slot_stride, seg_slot, cu_rows, decay_piece, n_pieces, piece_rows,       \
                        V * D, HVD);                                                                                  \
       if (err != cudaSuccess) return (int)err;                                                                       \
-      CBIS_RET_AS(NPL, LL, 16, kRetRows, kRetFromStarts, S * n_pieces);                                              \
+      CBIS_RET_AS(NPL, LL, CPT, kRetRows, kRetFromStarts, S * n_pieces);                                             \
       return (int)err;                                                                                               \
     }                                                                                                                \
     if (shorts) {                                                                                                    \
-      CBIS_RET_AS(NPL, LL, 32, kRetRowsShort, kRetWhole, S);                                                         \
+      CBIS_RET_AS(NPL, LL, 1, kRetRowsShort, kRetWhole, S);                                                          \
       return (int)err;                                                                                               \
     }                                                                                                                \
-    CBIS_RET_AS(NPL, LL, 16, kRetRows, kRetWhole, S);                                                                \
+    CBIS_RET_AS(NPL, LL, CPT, kRetRows, kRetWhole, S);                                                               \
     return (int)err;                                                                                                 \
   } while (0)
   if (L == 8) {

@@ -920,28 +920,53 @@ USE_QK_PREPARE = __import__("os").environ.get("CBIS_QK_PREPARE", "1") != "0"   #
 
 
 # A long segment of a retention layer is cut into pieces that run side by side where the step's blocks are few (one
-# prompt offers heads x columns / 16 of them, and its rows wait on one another): see ``retention``.
-RETENTION_PIECE_ROWS = 128            # rows of a piece (a multiple of the kernel's batches of 32 rows)
-RETENTION_PIECES_FROM = 384           # the longest segment of a step from which segments are cut
-RETENTION_PIECES_MAX_BLOCKS = 1184    # blocks of the uncut step (segments x heads x columns / 16) up to which they are: 8 a SM
+# prompt offers heads x columns / 64 of them, and its rows wait on one another): see ``retention``.
+RETENTION_PIECE_UNIT = 32             # a piece's rows are a multiple of this (and of the kernel's batches of 16 rows)
+RETENTION_PIECE_SIZES = 16            # piece sizes 32, 64, ... for which a mixer keeps decay^rows
+RETENTION_PIECES_FROM = 128           # the longest segment of a step from which segments are cut
+RETENTION_PIECES_MAX_BLOCKS = 160     # blocks of the uncut step (segments x heads x column blocks) up to which they are: about one a SM
+RETENTION_PIECES_BLOCKS_WANTED = 768  # blocks of the cut step that the piece size aims at
 RETENTION_PIECES_MAX_BYTES = 1 << 29  # the most scratch (start states of all pieces) a step may take
 
 
+def retention_piece_decays(decays):
+    """``[RETENTION_PIECE_SIZES, heads]`` 32-bit: row i holds decay^(32 (i + 1)) per head, made in 64-bit and rounded
+    once: what a whole piece of a cut segment takes off a state."""
+    return torch.tensor([[float(d) ** (RETENTION_PIECE_UNIT * (i + 1)) for d in decays] for i in range(RETENTION_PIECE_SIZES)],
+                        dtype=torch.float64).to(torch.float32)
+
+
+def retention_piece_rows(longest: int, n_segments: int, heads: int, dim: int, v_dim: int) -> int:
+    """Rows of a piece for a step whose longest segment has ``longest`` rows, 0 where segments stay whole: they are cut
+    where the uncut step has about a block a SM or fewer, into as many pieces as give RETENTION_PIECES_BLOCKS_WANTED
+    blocks (measured: with 32 blocks a segment 16 to 32 pieces are best, with 128 blocks 4 to 8, above 500 none)."""
+    blocks = n_segments * heads * -(-v_dim // (64 if dim <= 128 else 32))
+    if longest < RETENTION_PIECES_FROM or blocks > RETENTION_PIECES_MAX_BLOCKS:
+        return 0
+    want = max(2, RETENTION_PIECES_BLOCKS_WANTED // blocks)
+    rows = -(-(-(-longest // want)) // RETENTION_PIECE_UNIT) * RETENTION_PIECE_UNIT
+    rows = min(rows, RETENTION_PIECE_UNIT * RETENTION_PIECE_SIZES)
+    n = -(-longest // rows)
+    if n < 2 or n_segments * n > 65535 or n_segments * n * heads * v_dim * dim * 4 > RETENTION_PIECES_MAX_BYTES:
+        return 0
+    return rows
+
+
 def retention(qkv, q_off, k_off, v_off, positions, freqs, rot_dims, k_scale, one_minus_decay, state, seg_slot, cu_rows,
-              n_segments, heads, dim, v_dim, y, max_seg_rows: int = 0, decay_piece=None, piece_rows=None):
+              n_segments, heads, dim, v_dim, y, max_seg_rows: int = 0, piece_decays=None, piece_rows=None):
     """Retention over every segment's rows, from and into the requests' states: per head S <- decay S + k v^T,
     y = S^T q, after the first ``rot_dims`` entries of q and k were rotated in pairs (entry i with i + rot_dims/2) by
     position * freqs[i] and k was multiplied by ``k_scale``.  ``qkv``: the compute type, q | k | v at their column
     offsets; ``one_minus_decay``: 32-bit ``[heads]``, 1 - decay per head; ``y``: 32-bit ``[T, heads * v_dim]``;
     ``state``: 32-bit ``[slots, heads * v_dim * dim]``; ``max_seg_rows``: the step's longest segment if known.
 
-    A segment's rows are walked in order.  With ``decay_piece`` (32-bit ``[heads]``: decay^piece_rows, ``piece_rows``
-    defaulting to ``RETENTION_PIECE_ROWS``), where the step's longest segment is long and its blocks are few, segments
+    A segment's rows are walked in order.  With ``piece_decays`` (``retention_piece_decays`` of the heads' decays, on
+    the device), where the step's longest segment is long and its blocks are few (``retention_piece_rows``), segments
     are cut into pieces that run side by side: every piece's end state from zero, then the start states one after the
     other (start[p + 1] = decay^piece_rows start[p] + end[p]), then every piece again from its start state.  That is
-    twice the arithmetic for many times the parallel work; against the walk in one piece the results differ by
-    rounding only.  ``piece_rows=0``: never cut."""
-    _need_cuda(qkv, positions, freqs, one_minus_decay, state, seg_slot, cu_rows, y, decay_piece)
+    five thirds of the arithmetic for many times the parallel work; against the walk in one piece the results differ
+    by rounding only.  ``piece_rows``: a piece size of one's own (a multiple of 32 up to 512); 0: never cut."""
+    _need_cuda(qkv, positions, freqs, one_minus_decay, state, seg_slot, cu_rows, y, piece_decays)
     T = qkv.shape[0]
     assert qkv.stride(1) == 1 and positions.dtype == torch.int32 and positions.shape[0] >= T
     assert y.dtype == torch.float32 and y.stride(1) == 1 and y.shape == (T, heads * v_dim)
@@ -949,26 +974,21 @@ def retention(qkv, q_off, k_off, v_off, positions, freqs, rot_dims, k_scale, one
     assert one_minus_decay.dtype == torch.float32 and one_minus_decay.numel() == heads and one_minus_decay.is_contiguous()
     assert rot_dims == 0 or (freqs.dtype == torch.float32 and freqs.numel() >= rot_dims // 2 and freqs.is_contiguous())
     longest = int(max_seg_rows or 0)
-    n_pieces, starts = 1, None
-    if decay_piece is not None and piece_rows != 0:
-        assert decay_piece.dtype == torch.float32 and decay_piece.numel() == heads and decay_piece.is_contiguous()
-        explicit = piece_rows is not None
-        piece_rows = int(piece_rows) if explicit else RETENTION_PIECE_ROWS
-        assert piece_rows > 0 and piece_rows % 32 == 0
-        n = -(-longest // piece_rows)
-        per_state = heads * v_dim * dim
-        if n > 1 and (explicit or (longest >= RETENTION_PIECES_FROM
-                                   and n_segments * heads * -(-v_dim // 16) <= RETENTION_PIECES_MAX_BLOCKS
-                                   and n_segments * n * per_state * 4 <= RETENTION_PIECES_MAX_BYTES
-                                   and n_segments * n <= 65535)):
-            n_pieces = n
-            starts = torch.empty((n_segments * n_pieces, per_state), dtype=torch.float32, device=qkv.device)
+    n_pieces, rows, starts, decay_piece = 1, 0, None, None
+    if piece_decays is not None and piece_rows != 0 and longest > 0:
+        assert piece_decays.dtype == torch.float32 and piece_decays.shape == (RETENTION_PIECE_SIZES, heads) and piece_decays.is_contiguous()
+        rows = int(piece_rows) if piece_rows is not None else retention_piece_rows(longest, n_segments, heads, dim, v_dim)
+        assert rows >= 0 and rows % RETENTION_PIECE_UNIT == 0 and rows <= RETENTION_PIECE_UNIT * RETENTION_PIECE_SIZES
+        if rows and longest > rows:
+            n_pieces = -(-longest // rows)
+            decay_piece = piece_decays[rows // RETENTION_PIECE_UNIT - 1]
+            starts = torch.empty((n_segments * n_pieces, heads * v_dim * dim), dtype=torch.float32, device=qkv.device)
     st = kernels().cbis_retention(_ptr(qkv), c_int(qkv.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), _ptr(positions),
                                   _ptr(freqs), c_int(rot_dims), c_float(k_scale), _ptr(one_minus_decay), _ptr(state),
                                   ctypes.c_longlong(state.stride(0)), _ptr(seg_slot), _ptr(cu_rows), _ptr(y),
                                   c_int(y.stride(0)), c_int(n_segments), c_int(heads), c_int(dim), c_int(v_dim),
                                   c_int(dtype_code(qkv.dtype)), _stream(), c_int(longest), c_int(n_pieces),
-                                  c_int(piece_rows or 0), _ptr(starts), _ptr(decay_piece if n_pieces > 1 else None))
+                                  c_int(rows if n_pieces > 1 else 0), _ptr(starts), _ptr(decay_piece))
     _check(st, "retention", f"segments={n_segments} heads={heads} dim={dim} v_dim={v_dim} rot_dims={rot_dims} "
                             f"pieces={n_pieces}", launches=3 if n_pieces > 1 else 1)
 

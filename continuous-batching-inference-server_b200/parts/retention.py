@@ -46,7 +46,7 @@ class RetentionMixer(Mixer):
         self.k_scale = float(k_scale) if k_scale is not None else self.dim ** -0.5
         self.d_qk, self.d_v = self.heads * self.dim, self.heads * self.v_dim
         self.names = tuple(names)
-        self.w_in = self.w_out = self.freqs = self.one_minus_decay = self.decay_piece = None
+        self.w_in = self.w_out = self.freqs = self.one_minus_decay = self.piece_decays = None
 
     def state_need(self):
         return StateNeed((self.heads * self.v_dim * self.dim,), torch.float32)
@@ -64,9 +64,7 @@ class RetentionMixer(Mixer):
         self.freqs = rotary_frequencies(self.rot_base, self.rot_dims, self.rot_stretch).to(device)
         # 1 - decay in 64-bit, rounded once: a decay near 1 keeps its digits
         self.one_minus_decay = torch.tensor([1.0 - d for d in self.decays], dtype=torch.float64).to(torch.float32).to(device)
-        # what a whole piece of a cut segment takes off a state, in 64-bit, rounded once
-        self.decay_piece = torch.tensor([d ** ops.RETENTION_PIECE_ROWS for d in self.decays],
-                                        dtype=torch.float64).to(torch.float32).to(device)
+        self.piece_decays = ops.retention_piece_decays(self.decays).to(device)
 
     def streamed_weights(self):
         return [self.w_in, self.w_out]
@@ -77,7 +75,7 @@ class RetentionMixer(Mixer):
         y = torch.empty((T, self.d_v), dtype=torch.float32, device=h.device)
         ops.retention(proj, 0, self.d_qk, 2 * self.d_qk, ctx.positions, self.freqs, self.rot_dims, self.k_scale,
                       self.one_minus_decay, state, ctx.seg_slot, ctx.cu_rows, ctx.n_segments, self.heads, self.dim,
-                      self.v_dim, y, max_seg_rows=ctx.max_seg_rows, decay_piece=self.decay_piece)
+                      self.v_dim, y, max_seg_rows=ctx.max_seg_rows, piece_decays=self.piece_decays)
         g = torch.empty((T, self.d_v), dtype=h.dtype, device=h.device)
         g0 = 2 * self.d_qk + self.d_v
         ops.rms_norm(y, None, self.eps, g, parts=self.heads, gate=proj[:, g0:g0 + self.d_v], gate_act=self.gate_act,

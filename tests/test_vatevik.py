@@ -119,7 +119,7 @@ def test_long_segments_cut_into_pieces_that_run_side_by_side(H, D, V, dims, piec
     ks = D ** -0.5
     fd = torch.tensor(freqs, dtype=torch.float64).float().cuda()
     om = torch.tensor([1.0 - d for d in decays], dtype=torch.float64).float().cuda()
-    dp = torch.tensor([d ** piece for d in decays], dtype=torch.float64).float().cuda()
+    dp = ops.retention_piece_decays(decays).cuda()
     rows = [b + n for b, n in zip(before, lens)]
     qkv = [rounded(torch.randn(r, 2 * H * D + H * V, generator=g), dtype) for r in rows]
     refs, ends = [], []
@@ -146,7 +146,7 @@ def test_long_segments_cut_into_pieces_that_run_side_by_side(H, D, V, dims, piec
                           torch.tensor(pos, dtype=torch.int32, device="cuda"), fd, dims, ks, om, state,
                           torch.tensor(live, dtype=torch.int32, device="cuda"), torch.tensor(cu, dtype=torch.int32, device="cuda"),
                           len(live), H, D, V, y, max_seg_rows=max(segs[i].shape[0] for i in live),
-                          decay_piece=dp if part else None, piece_rows=piece_rows if part else 0)
+                          piece_decays=dp if part else None, piece_rows=piece_rows if part else 0)
             out.append((live, cu, y.double().cpu()))
         return out[1], state.double().cpu()
 
@@ -506,17 +506,17 @@ def test_a_long_prompt_whose_retention_runs_in_pieces():
     second from the state the first left), after a short portion, and in portions too short to be cut, all give the
     plain implementation's logits; one head never forgets, one forgets within a piece."""
     from cbis_b200.kernels import ops
-    n = ops.RETENTION_PIECES_FROM + 3 * ops.RETENTION_PIECE_ROWS + 37
+    n = 5 * ops.RETENTION_PIECES_FROM + 37
     cfgd = config(48, 50, [ret(3, 16, 24, [1.0, 0.96875, 0.9990234375], base=1000.0, mlp=dense(32)),
                            attn(2, 1, 16, 16, 0.25, mlp=None),
                            ret(2, 24, 16, [0.99951171875, 0.9], rot_dims=8, mlp=dense(24))])
     w = make_weights(cfgd, 21)
     toks = tokens_of(cfgd, n, 6)
     ref = plain(cfgd, w, toks)
-    half = ops.RETENTION_PIECES_FROM + ops.RETENTION_PIECE_ROWS + 1
+    half = 2 * ops.RETENTION_PIECES_FROM + 1
     for dtype in ("float32", "bfloat16"):
         eng = make_engine(cfgd, w, dtype, page_size=16, num_pages=-(-n // 16) + 4, max_batched_tokens=n + 8)
-        for sizes in ([n], [half, n - half], [5, n - 5], [200, 200, 200, n - 600]):
+        for sizes in ([n], [half, n - half], [5, n - 5], [200], [100]):       # the last: portions too short to be cut
             got = run_cut(eng, toks, sizes)
             err = (got - ref).abs().max(1).values
             if dtype == "float32":
