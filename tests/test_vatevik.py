@@ -53,7 +53,7 @@ def test_retention_recurrence_over_steps(H, D, V, dims, dtype):
     lens, starts = [37, 5, 18], [0, 900, 3]
     T = sum(lens)
     qkv = rounded(torch.randn(T, 3 + 2 * H * D + H * V, generator=g), dtype)
-    decays = [1.0, 0.5, 0.99951171875][:H] if H > 1 else [0.9901568667976963]
+    decays = [1.0, 0.5, 0.999755859375][:H] if H > 1 else [0.9873046875]
     freqs = pv.frequencies(31.0, dims) if dims else np.zeros(0)
     ks = D ** -0.5
     refs, at = [], 0
@@ -114,7 +114,7 @@ def test_long_segments_cut_into_pieces_that_run_side_by_side(H, D, V, dims, piec
     before = [5, 0, 40, 1, 0, 7]
     lens = [4 * piece + 9, piece, 3 * piece, 2 * piece + 1, 2 * piece - 1, 3]
     n_req = len(lens)
-    decays = [1.0, 0.96875, 0.99951171875][:H] if H > 1 else [0.9901568667976963]
+    decays = [1.0, 0.96875, 0.999755859375][:H] if H > 1 else [0.9873046875]
     freqs = pv.frequencies(10000.0, dims) if dims else np.zeros(0)
     ks = D ** -0.5
     fd = torch.tensor(freqs, dtype=torch.float64).float().cuda()
@@ -483,7 +483,7 @@ def test_far_tokens_held_by_a_slow_decay_and_long_decoding():
     """Retention whose decays are near one: the logits 300 tokens later still depend on the first token, in a whole
     prompt, in portions, and when the last 150 tokens are decoded one by one; the rounded decay's lost digits do not
     add up."""
-    cfgd = config(32, 40, [ret(2, 8, 12, [0.9984498036601873, 0.99951171875], base=1000.0, rot_dims=8, mlp=None)])
+    cfgd = config(32, 40, [ret(2, 8, 12, [0.998291015625, 0.999755859375], base=1000.0, rot_dims=8, mlp=None)])
     w = make_weights(cfgd, 8)
     toks = tokens_of(cfgd, 300, 4)
     ref = plain(cfgd, w, toks)
@@ -509,7 +509,7 @@ def test_a_long_prompt_whose_retention_runs_in_pieces():
     n = 5 * ops.RETENTION_PIECES_FROM + 37
     cfgd = config(48, 50, [ret(3, 16, 24, [1.0, 0.96875, 0.9990234375], base=1000.0, mlp=dense(32)),
                            attn(2, 1, 16, 16, 0.25, mlp=None),
-                           ret(2, 24, 16, [0.99951171875, 0.9], rot_dims=8, mlp=dense(24))])
+                           ret(2, 24, 16, [0.999755859375, 0.9], rot_dims=8, mlp=dense(24))])
     w = make_weights(cfgd, 21)
     toks = tokens_of(cfgd, n, 6)
     ref = plain(cfgd, w, toks)
