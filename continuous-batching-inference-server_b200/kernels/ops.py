@@ -936,11 +936,17 @@ def retention_piece_decays(decays):
                         dtype=torch.float64).to(torch.float32)
 
 
-def retention_piece_rows(longest: int, n_segments: int, heads: int, dim: int, v_dim: int) -> int:
+def retention_piece_rows(longest: int, n_segments: int, heads: int, dim: int, v_dim: int, total_rows: int = 0) -> int:
     """Rows of a piece for a step whose longest segment has ``longest`` rows, 0 where segments stay whole: they are cut
     where the uncut step has about a block a SM or fewer, into as many pieces as give RETENTION_PIECES_BLOCKS_WANTED
-    blocks (measured: with 32 blocks a segment 16 to 32 pieces are best, with 128 blocks 4 to 8, above 500 none)."""
-    blocks = n_segments * heads * -(-v_dim // (64 if dim <= 128 else 32))
+    blocks (measured: with 32 blocks a segment 16 to 32 pieces are best, with 128 blocks 4 to 8, above 500 none).
+    With ``total_rows`` the step counts as no more segments than its rows would fill at the longest one's length: a
+    prompt beside a few decoding rows is still one long walk."""
+    if total_rows > 0 and longest > 0:
+        n_long = min(n_segments, -(-total_rows // longest))
+    else:
+        n_long = n_segments
+    blocks = n_long * heads * -(-v_dim // (64 if dim <= 128 else 32))
     if longest < RETENTION_PIECES_FROM or blocks > RETENTION_PIECES_MAX_BLOCKS:
         return 0
     want = max(2, RETENTION_PIECES_BLOCKS_WANTED // blocks)
@@ -977,7 +983,7 @@ def retention(qkv, q_off, k_off, v_off, positions, freqs, rot_dims, k_scale, one
     n_pieces, rows, starts, decay_piece = 1, 0, None, None
     if piece_decays is not None and piece_rows != 0 and longest > 0:
         assert piece_decays.dtype == torch.float32 and piece_decays.shape == (RETENTION_PIECE_SIZES, heads) and piece_decays.is_contiguous()
-        rows = int(piece_rows) if piece_rows is not None else retention_piece_rows(longest, n_segments, heads, dim, v_dim)
+        rows = int(piece_rows) if piece_rows is not None else retention_piece_rows(longest, n_segments, heads, dim, v_dim, total_rows=T)
         assert rows >= 0 and rows % RETENTION_PIECE_UNIT == 0 and rows <= RETENTION_PIECE_UNIT * RETENTION_PIECE_SIZES
         if rows and longest > rows:
             n_pieces = -(-longest // rows)

@@ -501,6 +501,41 @@ def test_far_tokens_held_by_a_slow_decay_and_long_decoding():
                 assert err.max() < tol and err.median() < tol / 4, (sizes, err.max().item(), err.median().item())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_prompt_cut_into_pieces_beside_decoding_rows(dtype):
+    """One long segment beside five single rows from states of their own, the piece size chosen by the step: the long
+    one is cut (the step counts as one long walk), the single rows walk as ever, and all agree with the uncut step."""
+    from cbis_b200.kernels import ops
+    H, D, V, n = 3, 32, 48, 300
+    g = torch.Generator().manual_seed(12)
+    decays = [1.0, 0.9375, 0.998291015625]
+    lens = [1, 1, n, 1, 1, 1]
+    T = sum(lens)
+    assert ops.retention_piece_rows(n, len(lens), H, D, V, total_rows=T) > 0
+    qkv = dev(torch.randn(T, 2 * H * D + H * V, generator=g), dtype)
+    freqs = torch.tensor(pv.frequencies(10000.0, D), dtype=torch.float64).float().cuda()
+    om = torch.tensor([1.0 - d for d in decays], dtype=torch.float64).float().cuda()
+    dp = ops.retention_piece_decays(decays).cuda()
+    cu = torch.tensor(np.cumsum([0] + lens), dtype=torch.int32, device="cuda")
+    pos = torch.cat([torch.arange(m) + (0 if m > 1 else 77 + i) for i, m in enumerate(lens)]).to(torch.int32).cuda()
+    slots = torch.tensor([4, 0, 2, 5, 1, 3], dtype=torch.int32, device="cuda")
+    state0 = torch.randn(6, H * V * D, generator=g).cuda()
+    state0[2].zero_()
+    out = []
+    for piece_rows in (None, 0):
+        state = state0.clone()
+        y = torch.empty(T, H * V, dtype=torch.float32, device="cuda")
+        ops.retention(qkv, 0, H * D, 2 * H * D, pos, freqs, D, D ** -0.5, om, state, slots, cu, len(lens), H, D, V, y,
+                      max_seg_rows=n, piece_decays=dp, piece_rows=piece_rows)
+        out.append((y.double().cpu(), state.double().cpu()))
+    (y_cut, s_cut), (y_one, s_one) = out
+    assert (y_cut - y_one).abs().max() < 2e-5 * max(1.0, y_one.abs().max().item())
+    assert (s_cut - s_one).abs().max() < 2e-5 * max(1.0, s_one.abs().max().item())
+    single = [i for i in range(T) if not 2 <= i < 2 + n]
+    assert torch.equal(y_cut[single], y_one[single])            # a single row is one piece: the same bits
+    assert not torch.equal(s_one, state0.double().cpu())
+
+
 def test_a_long_prompt_whose_retention_runs_in_pieces():
     """A prompt long enough that the engine cuts its retention segments into pieces: whole, in two long portions (the
     second from the state the first left), after a short portion, and in portions too short to be cut, all give the

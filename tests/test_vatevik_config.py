@@ -151,3 +151,27 @@ def test_random_weights_keep_activations_in_range():
     logits, stream = pv.forward(MIXED, as_numpy(w), list(range(20)))
     assert np.isfinite(logits).all() and 0.1 < np.abs(stream[-1]).mean() < 50
     assert np.abs(logits).max() < MIXED["logit_softcap"]
+
+
+def test_where_long_retention_segments_are_cut_into_pieces():
+    """The piece size of a step: none for short segments or where the uncut step fills the SMs, a multiple of 32 that
+    gives at least two pieces otherwise; a prompt beside decoding rows counts as the one long walk it is; the table of
+    decays holds decay^(32 (i + 1)), rounded once from 64-bit."""
+    import torch
+    from cbis_b200.kernels import ops
+    assert ops.retention_piece_rows(100, 1, 8, 128, 256) == 0                   # short
+    assert ops.retention_piece_rows(4096, 64, 8, 128, 256) == 0                 # many long segments: whole
+    for longest, segs in ((128, 1), (500, 1), (3000, 1), (700, 4), (100000, 1)):
+        rows = ops.retention_piece_rows(longest, segs, 8, 128, 256)
+        assert rows > 0 and rows % 32 == 0 and rows <= 32 * ops.RETENTION_PIECE_SIZES and -(-longest // rows) >= 2
+    assert ops.retention_piece_rows(3000, 40, 8, 128, 256) == 0
+    assert ops.retention_piece_rows(3000, 40, 8, 128, 256, total_rows=3039) > 0      # one prompt beside 39 decoding rows
+    assert ops.retention_piece_rows(3000, 40, 8, 128, 256, total_rows=40 * 3000) == 0
+    assert ops.retention_piece_rows(3000, 1, 4, 512, 512) == 0 or \
+        -(-3000 // ops.retention_piece_rows(3000, 1, 4, 512, 512)) * 4 * 512 * 512 * 4 <= ops.RETENTION_PIECES_MAX_BYTES
+    decays = [1.0, 0.5, 0.9873046875]
+    table = ops.retention_piece_decays(decays)
+    assert table.shape == (ops.RETENTION_PIECE_SIZES, 3) and table.dtype == torch.float32
+    for i in (0, 3, ops.RETENTION_PIECE_SIZES - 1):
+        for h, d in enumerate(decays):
+            assert table[i, h].item() == torch.tensor(d ** (32 * (i + 1)), dtype=torch.float64).float().item()
