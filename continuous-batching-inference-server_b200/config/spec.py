@@ -44,6 +44,10 @@ class LayerSpec:
     post_norm_mixer: Optional[PartSpec] = None
     post_norm_feed_forward: Optional[PartSpec] = None
     post_norm_prefixes: Tuple[str, str] = ("post_1.", "post_2.")
+    # a constant on everything the layer adds to the stream (1: none), and a third part after the feed-forward that
+    # reads the stream as it is (a feed-forward kind; None: the layer has none); for the arrangements that know them
+    residual_scale: float = 1.0
+    side: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

@@ -54,7 +54,7 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
   const int hk = h / (n_head / n_kv_head);
   const int pos = positions[row];
   const int kend = pos + 1;
-  const int kstart = window > 0 ? max(0, kend - window) : 0;
+  const int kstart = first_seen(pos, window);
   const int per = (((kend - kstart) + nsplit - 1) / nsplit + 31) & ~31;
   const int ks = kstart + split * per;
   const int ke = min(kend, ks + per);

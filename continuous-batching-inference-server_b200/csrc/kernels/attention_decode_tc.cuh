@@ -108,7 +108,7 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
   const int hk = h / (n_head / n_kv_head);
   const int pos = positions[row];
   const int kend = pos + 1;
-  const int kstart = window > 0 ? max(0, kend - window) : 0;
+  const int kstart = first_seen(pos, window);
   const int first_tile = kstart >> 4;
   const int per = (((kend - (first_tile << 4)) + nsplit - 1) / nsplit + 31) & ~31;   // keys per split, whole tiles
   const int ks = (first_tile << 4) + split * per;

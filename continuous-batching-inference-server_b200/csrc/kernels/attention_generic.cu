@@ -100,7 +100,7 @@ __global__ void paged_attention_generic_kernel(
   const float slope = slopes ? slopes[h] : 0.f;
   const int* bt = block_table + (size_t)seq * max_blocks;
   int kend = pos + 1;
-  int kstart = window > 0 ? max(0, kend - window) : 0;
+  int kstart = first_seen(pos, window);
   if (n_chunks > 1) {   // this warp's share of the keys: chunks by absolute index, merged by a second kernel
     kstart = max(kstart, chunk * chunk_keys);
     kend = min(kend, (chunk + 1) * chunk_keys);

@@ -24,7 +24,7 @@ prefill_merge_kernel(const float* partial, const int* positions, const int* row_
   const int row = row0 + blockIdx.x;
   if (row_seq && row_seq[row] < 0) return;   // a padding row of a fixed-size batch: nothing was computed for it
   const int p = positions[row];
-  const int c_lo = (window > 0 ? max(0, p - window + 1) : 0) / chunk_keys, c_hi = p / chunk_keys;
+  const int c_lo = first_seen(p, window) / chunk_keys, c_hi = p / chunk_keys;
   const int units = n_head * (hd / 4);
   for (int u = threadIdx.x; u < units; u += blockDim.x) {
     const int h = u / (hd / 4), d = (u % (hd / 4)) * 4;

@@ -89,7 +89,7 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
   const int pos0 = seg_start[seg] + tile * PF_BM;           // position of the tile's first row
   const int rows_here = min(PF_BM, n_rows - tile * PF_BM);
   int kend = pos0 + rows_here;                              // keys 0 .. kend-1 can matter to this tile
-  int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int kbegin = first_seen(pos0, window);
   if (n_chunks > 1) {   // this block's share of the keys (chunks by absolute index, whole key tiles)
     kbegin = max(kbegin, chunk * chunk_keys);
     kend = min(kend, (chunk + 1) * chunk_keys);
@@ -100,6 +100,7 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
   // this thread's two rows: g and g + 8 of the warp's 16
   const int lr0 = warp * 16 + g, lr1 = lr0 + 8;
   const int p0 = pos0 + lr0, p1 = pos0 + lr1;
+  const int lo0 = first_seen(p0, window), lo1 = first_seen(p1, window);      // the first key each of the two rows sees
   uint32_t qf[KS][4];
   {
     const __nv_bfloat16* q0 = q + (size_t)(r_begin + tile * PF_BM + lr0) * q_ld + h * hdk;
@@ -179,7 +180,7 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
     }
     // scale (into the base-2 domain), mask, running max
     const int j0 = kt * PF_BN;
-    const bool edge = (j0 + PF_BN - 1 > pos0) || (window > 0 && j0 < pos0 + PF_BM - window + 1);
+    const bool edge = (j0 + PF_BN - 1 > pos0) || (window != 0 && j0 < first_seen(pos0 + PF_BM - 1, window));
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
     for (int nt = 0; nt < PF_BN / 8; ++nt)
@@ -192,8 +193,8 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
           b2 = fmaf(-slope2, (float)(p1 - j), b2);
         }
         if (edge) {
-          if (j > p0 || (window > 0 && j < p0 - window + 1)) a = -INFINITY;
-          if (j > p1 || (window > 0 && j < p1 - window + 1)) b2 = -INFINITY;
+          if (j > p0 || j < lo0) a = -INFINITY;
+          if (j > p1 || j < lo1) b2 = -INFINITY;
         }
         s[nt][e] = a;
         s[nt][2 + e] = b2;

@@ -47,7 +47,7 @@ paged_prefill_f32_kernel(const float* q, int q_ld, const float* kc, const float*
   const int pos0 = seg_start[seg] + tile * F_BM;
   const int rows_here = min(F_BM, n_rows - tile * F_BM);
   int kend = pos0 + rows_here;
-  int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int kbegin = first_seen(pos0, window);
   if (n_chunks > 1) {   // this block's share of the keys; a chunk wholly outside the rows' range leaves nothing
     kbegin = max(kbegin, chunk * chunk_keys);
     kend = min(kend, (chunk + 1) * chunk_keys);
@@ -121,7 +121,7 @@ paged_prefill_f32_kernel(const float* q, int q_ld, const float* kc, const float*
 #pragma unroll
       for (int u = 0; u < F_BN / 4; ++u) {
         const int j = j0 + part + 4 * u;
-        const bool seen = j <= p2[w] && j < kend && (window == 0 || j >= p2[w] - window + 1);
+        const bool seen = j <= p2[w] && j < kend && j >= first_seen(p2[w], window);
         s[w][u] = seen ? s[w][u] * scale : -INFINITY;
         mx = fmaxf(mx, s[w][u]);
       }

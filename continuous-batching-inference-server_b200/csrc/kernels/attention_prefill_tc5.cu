@@ -199,7 +199,7 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int pos0 = seg_start[seg] + tile * BM;
   const int rows_here = min(BM, n_rows - tile * BM);
   int kend = pos0 + rows_here;
-  int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int kbegin = first_seen(pos0, window);
   if (n_chunks > 1) {   // few rows behind a long context: this cluster takes one chunk of the keys (whole key tiles,
                         // by absolute index) and leaves an unnormalised partial result for the merge kernel
     kbegin = max(kbegin, chunk * chunk_keys);
@@ -362,11 +362,11 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float v[BN];
       tmem_ld64(tmem_s + (j & 1) * BN + lane_addr, v);
-      const bool edge = (j0 + BN - 1 > pos0) || (window > 0 && j0 < pos0 + BM - window + 1) || j0 + BN > kend;
+      const bool edge = (j0 + BN - 1 > pos0) || (window != 0 && j0 < first_seen(pos0 + BM - 1, window)) || j0 + BN > kend;
       if (edge) {
         // keys this row may see in this tile: [lo, hi), as columns of the tile
         const int hi = min(min(p + 1, kend) - j0, BN);
-        const int lo = window > 0 ? max(p - window + 1 - j0, 0) : 0;
+        const int lo = max(first_seen(p, window) - j0, 0);
 #pragma unroll
         for (int i = 0; i < BN; ++i)
           if (i < lo || i >= hi) v[i] = -INFINITY;

@@ -22,6 +22,7 @@
 #define CBIS_ACT_GELU_TANH 2
 #define CBIS_ACT_SILU 3
 #define CBIS_ACT_SIGMOID 4
+#define CBIS_ACT_RELU2 5      // relu(v)^2
 
 #define CBIS_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -95,6 +96,13 @@ __device__ __forceinline__ void prefetch_share(const void* p, unsigned long long
   }
 }
 
+// Which keys the query at position p sees beside the causal rule, told by ONE signed number `window`: 0: every key up to
+// its own; w > 0: its own and the w - 1 before it (a sliding window); w < 0: those of its own block of -w positions,
+// blocks counted from position 0 of the sequence (wherever a prompt was cut).  The first key seen; never decreases with p.
+__device__ __forceinline__ int first_seen(int p, int window) {
+  return window > 0 ? max(0, p - window + 1) : (window < 0 ? p - p % (-window) : 0);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ void from_f32(float& dst, float v) { dst = v; }
@@ -133,6 +141,7 @@ __device__ __forceinline__ float sigmoid_f32(float v) { return 1.0f / (1.0f + ex
 __device__ __forceinline__ float activate(float v, int act) {
   if (act == CBIS_ACT_SILU) return v * sigmoid_f32(v);
   if (act == CBIS_ACT_SIGMOID) return sigmoid_f32(v);
+  if (act == CBIS_ACT_RELU2) return v > 0.f ? v * v : 0.f;
   if (act == CBIS_ACT_GELU_ERF) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
   if (act == CBIS_ACT_GELU_TANH) {
     const float c = 0.7978845608028654f;  // sqrt(2/pi)

@@ -46,17 +46,26 @@ __global__ void rms_norm_kernel(const TI* x, int x_ld, const TG* gate, int gate_
   }
 }
 
-// out[r, c] = act(a[r, c]) * b[r, c]
+// out[r, c] = act(a[r, c]) * b[r, c]; with `b_rows` b's row is b_rows[r] instead (rows of a table looked up by token;
+// an index outside 0 .. b_n_rows - 1 reads as zeros)
 template <typename TT>
 __global__ void gate_mul_kernel(const TT* a, int a_ld, const TT* b, int b_ld, TT* out, int out_ld, int act, int rows,
-                                int n) {
+                                int n, const int* b_rows, int b_n_rows) {
   pdl_trigger();
   pdl_wait();
   const size_t total = (size_t)rows * n;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / n;
     const int c = (int)(i % n);
-    from_f32(out[r * out_ld + c], activate(to_f32(a[r * a_ld + c]), act) * to_f32(b[r * b_ld + c]));
+    size_t br = r;
+    bool there = true;
+    if (b_rows) {
+      const int t = b_rows[r];
+      there = t >= 0 && t < b_n_rows;
+      br = there ? (size_t)t : 0;
+    }
+    const float bv = there ? to_f32(b[br * b_ld + c]) : 0.f;
+    from_f32(out[r * out_ld + c], activate(to_f32(a[r * a_ld + c]), act) * bv);
   }
 }
 
@@ -92,7 +101,7 @@ CBIS_EXPORT int cbis_rms_norm(const void* x, int x_ld, int x_dtype, const void* 
 }
 
 CBIS_EXPORT int cbis_gate_mul(const void* a, int a_ld, const void* b, int b_ld, void* out, int out_ld, int act, int rows,
-                              int n, int dtype, void* stream) {
+                              int n, int dtype, void* stream, const int* b_rows, int b_n_rows) {
   if (rows <= 0 || n <= 0) return CBIS_OK;
   const size_t total = (size_t)rows * n;
   size_t blocks = (total + 255) / 256;
@@ -100,9 +109,9 @@ CBIS_EXPORT int cbis_gate_mul(const void* a, int a_ld, const void* b, int b_ld, 
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == CBIS_F32)
     return (int)launch_pdl(gate_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, st, (const float*)a, a_ld,
-                           (const float*)b, b_ld, (float*)out, out_ld, act, rows, n);
+                           (const float*)b, b_ld, (float*)out, out_ld, act, rows, n, b_rows, b_n_rows);
   if (dtype == CBIS_BF16)
     return (int)launch_pdl(gate_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, st, (const __nv_bfloat16*)a,
-                           a_ld, (const __nv_bfloat16*)b, b_ld, (__nv_bfloat16*)out, out_ld, act, rows, n);
+                           a_ld, (const __nv_bfloat16*)b, b_ld, (__nv_bfloat16*)out, out_ld, act, rows, n, b_rows, b_n_rows);
   return CBIS_ERR_BAD_DTYPE;
 }

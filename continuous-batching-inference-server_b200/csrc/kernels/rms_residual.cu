@@ -4,6 +4,7 @@
 //   stream's row is normalised for the next part, all in one pass over the row:
 //     d = delta[s,:] (+ delta_bias)                                           what the part before left
 //     if post_w: d = d / sqrt(mean(d^2) + post_eps) * (post_offset + post_w)   a norm AFTER the part
+//     d = d * delta_scale                                                      a constant on everything that is added
 //     v = x[s,:] + d;  x[s,:] = v                                             the stream moves on (32-bit)
 //     out[r,:] = v / sqrt(mean(v^2) + eps) * (offset + w)                      the norm BEFORE the next part
 //   offset 1 is for weights stored around zero, offset 0 for weights stored as they are applied.  With `rows` only
@@ -18,7 +19,7 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* x, const TD* delta, int delta_ld, const float* __restrict__ delta_bias,
                                    const float* __restrict__ post_w, float post_eps, float post_offset,
                                    const float* __restrict__ w, float eps, float offset, TO* out, const int* rows,
-                                   int d) {
+                                   int d, float delta_scale) {
   extern __shared__ float smem[];
   float* row = smem;           // d floats
   float* dl = smem + d;        // d floats
@@ -39,11 +40,12 @@ __global__ void add_rmsnorm_kernel(float* x, const TD* delta, int delta_ld, cons
       ss += v * v;
     }
     if (post_w) dscale = 1.0f / sqrtf(block_sum(ss, red) / (float)d + post_eps);
+    dscale *= delta_scale;
   }
   float ss = 0.f;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float v = xrow[c];
-    if (drow) v += post_w ? dl[c] * dscale * (post_offset + post_w[c]) : dl[c];
+    if (drow) v += post_w ? dl[c] * dscale * (post_offset + post_w[c]) : dl[c] * dscale;
     row[c] = v;
     ss += v * v;
   }
@@ -84,7 +86,7 @@ template <typename TD, typename TO, int NV>
 __global__ void __launch_bounds__(128)
 add_rmsnorm_reg_kernel(float* x, const TD* delta, int delta_ld, const float* __restrict__ delta_bias,
                        const float* __restrict__ post_w, float post_eps, float post_offset, const float* __restrict__ w,
-                       float eps, float offset, TO* out, const int* rows, int d) {
+                       float eps, float offset, TO* out, const int* rows, int d, float delta_scale) {
   __shared__ float red[33];
   pdl_trigger();
   const int nvec = d >> 2;
@@ -121,6 +123,7 @@ add_rmsnorm_reg_kernel(float* x, const TD* delta, int delta_ld, const float* __r
   }
   float dscale = 1.f;
   if (drow && post_w) dscale = 1.0f / sqrtf(block_sum(ssd, red) / (float)d + post_eps);
+  dscale *= delta_scale;
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -132,7 +135,7 @@ add_rmsnorm_reg_kernel(float* x, const TD* delta, int delta_ld, const float* __r
           v[i].z += dl[i].z * dscale * (post_offset + pw[i].z);
           v[i].w += dl[i].w * dscale * (post_offset + pw[i].w);
         } else {
-          v[i].x += dl[i].x; v[i].y += dl[i].y; v[i].z += dl[i].z; v[i].w += dl[i].w;
+          v[i].x += dl[i].x * dscale; v[i].y += dl[i].y * dscale; v[i].z += dl[i].z * dscale; v[i].w += dl[i].w * dscale;
         }
       }
       ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
@@ -164,7 +167,8 @@ CBIS_EXPORT int cbis_rms_residual_max_width() { return (200 * 1024 / 4 - 64) / 2
 // x: 32-bit [*, d]; delta (may be null): [*, delta_ld] of delta_dtype; out (may be null): [n, d] of out_dtype.
 CBIS_EXPORT int cbis_add_rmsnorm(float* x, const void* delta, int delta_ld, int delta_dtype, const float* delta_bias,
                                  const float* post_w, float post_eps, float post_offset, const float* w, float eps,
-                                 float offset, void* out, int out_dtype, const int* rows, int n, int d, void* stream) {
+                                 float offset, void* out, int out_dtype, const int* rows, int n, int d, void* stream,
+                                 float delta_scale) {
   if (n <= 0) return CBIS_OK;
   if (d <= 0 || d > cbis_rms_residual_max_width()) return CBIS_ERR_BAD_SIZE;
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
@@ -175,7 +179,7 @@ CBIS_EXPORT int cbis_add_rmsnorm(float* x, const void* delta, int delta_ld, int 
     if (smem > 48 * 1024)                                                                                             \
       cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
     return (int)launch_pdl(add_rmsnorm_kernel<TD, TO>, dim3(n), dim3(threads), smem, st, x, (const TD*)delta, delta_ld, \
-                           delta_bias, post_w, post_eps, post_offset, w, eps, offset, (TO*)out, rows, d);             \
+                           delta_bias, post_w, post_eps, post_offset, w, eps, offset, (TO*)out, rows, d, delta_scale); \
   } while (0)
   const int dd = delta ? delta_dtype : CBIS_F32;
   // rows in registers where every piece is 16 bytes wide and aligned
@@ -185,7 +189,7 @@ CBIS_EXPORT int cbis_add_rmsnorm(float* x, const void* delta, int delta_ld, int 
                    (!out || !((uintptr_t)out & (4 * esz_o - 1)));
 #define CBIS_ARN_REG(TD, TO, NV)                                                                                       \
   return (int)launch_pdl(add_rmsnorm_reg_kernel<TD, TO, NV>, dim3(n), dim3(128), 0, st, x, (const TD*)delta, delta_ld, \
-                         delta_bias, post_w, post_eps, post_offset, w, eps, offset, (TO*)out, rows, d)
+                         delta_bias, post_w, post_eps, post_offset, w, eps, offset, (TO*)out, rows, d, delta_scale)
 #define CBIS_ARN_PICK(TD, TO)                 \
   do {                                        \
     if (d <= 512) CBIS_ARN_REG(TD, TO, 1);    \

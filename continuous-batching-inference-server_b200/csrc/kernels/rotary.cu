@@ -3,6 +3,9 @@
 //   rope_rows: in every row r (position p = positions[r]) and every head, `dims` entries starting at a column are
 //   rotated in pairs: entry i with entry i + dims/2 ("rotate half"), by the angle p * base^(-2 i / dims):
 //     (u, v) -> (u cos a - v sin a, v cos a + u sin a).
+//   With `neighbours` the pairs are the entries 2i and 2i + 1 instead; `length` multiplies cosine and sine (a rotation
+//   that also stretches).  With `keep` >= 0 the heads from `keep_head0` on are ALSO written as they came, unrotated,
+//   at dst column keep + (head - keep_head0) * width (a mixer whose values are its keys before the rotation).
 //   Source and destination may be different buffers with different strides between heads (a head's rotated part is
 //   moved to its place among the columns the attention kernel reads); entries beyond `dims` up to `width` are copied.
 //   head_gate_mul: out[r, h, :] = x[r, h, :] * sigmoid(gate[r, h]), one number per row and head.
@@ -21,7 +24,7 @@ namespace cbis {
 template <typename TT>
 __global__ void rope_rows_kernel(const TT* src, int src_ld, int src_col0, int src_head_stride, TT* dst, int dst_ld,
                                  int dst_col0, int dst_head_stride, const int* positions, int heads, int width, int dims,
-                                 const float* __restrict__ freqs) {
+                                 const float* __restrict__ freqs, int neighbours, float length, int keep, int keep_head0) {
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
@@ -34,15 +37,26 @@ __global__ void rope_rows_kernel(const TT* src, int src_ld, int src_col0, int sr
     const int h = u / per_head, i = u % per_head;
     const TT* sh = s0 + (size_t)h * src_head_stride;
     TT* dh = d0 + (size_t)h * dst_head_stride;
+    TT* kp = (keep >= 0 && h >= keep_head0) ? dst + (size_t)r * dst_ld + keep + (size_t)(h - keep_head0) * width : nullptr;
     if (i < half) {
       float sn, cs;
       sincosf(p * freqs[i], &sn, &cs);
-      const float a = to_f32(sh[i]), b = to_f32(sh[i + half]);
-      from_f32(dh[i], a * cs - b * sn);
-      from_f32(dh[i + half], b * cs + a * sn);
+      const int c0 = neighbours ? 2 * i : i, c1 = neighbours ? 2 * i + 1 : i + half;
+      const TT ra = sh[c0], rb = sh[c1];
+      const float a = to_f32(ra), b = to_f32(rb);
+      cs *= length;
+      sn *= length;
+      if (kp) {           // before the rotated values are stored: source and destination may be one buffer
+        kp[c0] = ra;
+        kp[c1] = rb;
+      }
+      from_f32(dh[c0], a * cs - b * sn);
+      from_f32(dh[c1], b * cs + a * sn);
     } else {
       const int c = dims + (i - half);
-      dh[c] = sh[c];
+      const TT v = sh[c];
+      if (kp) kp[c] = v;
+      dh[c] = v;
     }
   }
 }
@@ -189,7 +203,8 @@ CBIS_EXPORT int cbis_blend_rows(const void* a, int a_ld, const void* b, int b_ld
 
 CBIS_EXPORT int cbis_rope_rows(const void* src, int src_ld, int src_col0, int src_head_stride, void* dst, int dst_ld,
                                int dst_col0, int dst_head_stride, const int* positions, int rows, int heads, int width,
-                               int dims, const float* freqs, int dtype, void* stream) {
+                               int dims, const float* freqs, int dtype, void* stream, int neighbours, float length,
+                               int keep, int keep_head0) {
   if (rows <= 0 || heads <= 0 || width <= 0) return CBIS_OK;
   if (dims < 0 || dims > width || dims % 2 || (dims > 0 && !freqs)) return CBIS_ERR_BAD_SIZE;
   const int units = heads * (dims / 2 + width - dims);
@@ -198,11 +213,11 @@ CBIS_EXPORT int cbis_rope_rows(const void* src, int src_ld, int src_col0, int sr
   if (dtype == CBIS_F32)
     return (int)launch_pdl(rope_rows_kernel<float>, dim3(rows), dim3(threads), 0, st, (const float*)src, src_ld, src_col0,
                            src_head_stride, (float*)dst, dst_ld, dst_col0, dst_head_stride, positions, heads, width, dims,
-                           freqs);
+                           freqs, neighbours, length, keep, keep_head0);
   if (dtype == CBIS_BF16)
     return (int)launch_pdl(rope_rows_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, st, (const __nv_bfloat16*)src,
                            src_ld, src_col0, src_head_stride, (__nv_bfloat16*)dst, dst_ld, dst_col0, dst_head_stride,
-                           positions, heads, width, dims, freqs);
+                           positions, heads, width, dims, freqs, neighbours, length, keep, keep_head0);
   return CBIS_ERR_BAD_DTYPE;
 }
 

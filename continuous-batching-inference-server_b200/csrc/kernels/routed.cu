@@ -15,7 +15,7 @@ constexpr int kScoreSigmoid = 0, kScoreSoftmax = 1;
 template <typename TT>
 __global__ void __launch_bounds__(256)
 route_topk_kernel(const TT* h, int h_ld, const TT* __restrict__ router, int* ids, float* weights, int W, int E, int top,
-                  int score, int renormalize) {
+                  int score, int renormalize, float renorm_eps, float weight_scale) {
   extern __shared__ float z[];
   pdl_trigger();
   pdl_wait();
@@ -80,8 +80,10 @@ route_topk_kernel(const TT* h, int h_ld, const TT* __restrict__ router, int* ids
     }
     __syncwarp();
   }
-  if (renormalize && lane == 0)
-    for (int k = 0; k < top; ++k) weights[(size_t)r * top + k] /= total;
+  if (lane == 0 && (renormalize || weight_scale != 1.f)) {
+    const float f = renormalize ? weight_scale / (total + renorm_eps) : weight_scale;
+    for (int k = 0; k < top; ++k) weights[(size_t)r * top + k] *= f;
+  }
 }
 
 // grid (pairs, ceil(F / 8)), 256 threads = 8 warps, a warp per hidden column f of pair (row, choice):
@@ -407,7 +409,8 @@ CBIS_EXPORT int cbis_routed_tiles(const void* h, int h_ld, const void* gate_up, 
 }
 
 CBIS_EXPORT int cbis_route_topk(const void* h, int h_ld, const void* router, int* ids, float* weights, int rows, int W,
-                                int E, int top, int score, int renormalize, int dtype, void* stream) {
+                                int E, int top, int score, int renormalize, int dtype, void* stream, float renorm_eps,
+                                float weight_scale) {
   if (rows <= 0) return CBIS_OK;
   if (W <= 0 || E <= 0 || top <= 0 || top > E || (score != kScoreSigmoid && score != kScoreSoftmax)) return CBIS_ERR_BAD_SIZE;
   if (E > 8192) return CBIS_ERR_TOO_LARGE;
@@ -415,10 +418,11 @@ CBIS_EXPORT int cbis_route_topk(const void* h, int h_ld, const void* router, int
   const size_t smem = (size_t)E * sizeof(float);
   if (dtype == CBIS_F32)
     return (int)launch_pdl(route_topk_kernel<float>, dim3(rows), dim3(256), smem, st, (const float*)h, h_ld,
-                           (const float*)router, ids, weights, W, E, top, score, renormalize);
+                           (const float*)router, ids, weights, W, E, top, score, renormalize, renorm_eps, weight_scale);
   if (dtype == CBIS_BF16)
     return (int)launch_pdl(route_topk_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, st, (const __nv_bfloat16*)h, h_ld,
-                           (const __nv_bfloat16*)router, ids, weights, W, E, top, score, renormalize);
+                           (const __nv_bfloat16*)router, ids, weights, W, E, top, score, renormalize, renorm_eps,
+                           weight_scale);
   return CBIS_ERR_BAD_DTYPE;
 }
 

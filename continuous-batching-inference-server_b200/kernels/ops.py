@@ -17,7 +17,7 @@ import torch
 from .library import kernels, optional_kernels
 
 F32, BF16 = 0, 1
-ACT = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2, "silu": 3, "sigmoid": 4}
+ACT = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2, "silu": 3, "sigmoid": 4, "relu2": 5}      # relu2: relu(v)^2
 
 _STATUS = {-1: "unsupported dtype", -2: "a size that the kernel does not take",
            -3: "misaligned pointer or stride", -4: "size too large for this kernel"}
@@ -811,15 +811,18 @@ def rms_norm(x, weight, eps, out, parts: int = 1, gate=None, gate_act="silu", ga
     _check(st, "rms_norm", f"rows={rows} width={n} parts={parts}")
 
 
-def gate_mul(a, b, act, out):
+def gate_mul(a, b, act, out, b_rows=None):
     """out = act(a) * b element by element (32-bit arithmetic, one rounding); a, b, out: ``[rows, n]`` of one type,
-    views with unit column stride are fine."""
-    _need_cuda(a, b, out)
+    views with unit column stride are fine.  With ``b_rows`` (int32, one per row) b is a table ``[*, n]`` and row r
+    takes b[b_rows[r]] (a token's row of a table; an index outside the table reads as zeros)."""
+    _need_cuda(a, b, out, b_rows)
     rows, n = a.shape
-    assert b.shape == a.shape and out.shape == a.shape and a.dtype == b.dtype == out.dtype
+    assert out.shape == a.shape and a.dtype == b.dtype == out.dtype and b.shape[1] == n
+    assert b.shape == a.shape if b_rows is None else (b_rows.dtype == torch.int32 and b_rows.shape[0] >= rows)
     assert a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1
     st = kernels().cbis_gate_mul(_ptr(a), c_int(a.stride(0)), _ptr(b), c_int(b.stride(0)), _ptr(out), c_int(out.stride(0)),
-                                 c_int(ACT[act]), c_int(rows), c_int(n), c_int(dtype_code(a.dtype)), _stream())
+                                 c_int(ACT[act]), c_int(rows), c_int(n), c_int(dtype_code(a.dtype)), _stream(),
+                                 _ptr(b_rows), c_int(b.shape[0]))
     _check(st, "gate_mul", f"rows={rows} n={n}")
 
 
@@ -827,12 +830,12 @@ RMS_RESIDUAL_MAX_WIDTH = (200 * 1024 // 4 - 64) // 2     # the widest row add_rm
 MATRIX_MEMORY_MAX_DIM = 512                              # the widest key of the matrix memory (cbis_matrix_memory_max_dim())
 
 
-def add_rmsnorm(x, delta, delta_bias, post, weight, eps, offset, out, rows=None):
+def add_rmsnorm(x, delta, delta_bias, post, weight, eps, offset, out, rows=None, delta_scale: float = 1.0):
     """One pass over the rows of the 32-bit residual stream ``x``: what a part left (``delta``, 32-bit or the compute
     type, plus ``delta_bias`` per column) is, with ``post`` = (weight, eps, offset), first divided by its own root mean
     square and multiplied by (offset + weight); it is added to x in place; and ``out`` takes x / sqrt(mean(x^2) + eps)
     * (offset + weight) (``weight`` None: x itself; ``out`` None: nothing).  With ``rows`` (int32) only those rows
-    are produced and x is not changed."""
+    are produced and x is not changed.  ``delta_scale`` multiplies what is added (after its own norm, if it has one)."""
     _need_cuda(x, delta, delta_bias, weight, out, rows)
     d = x.shape[1]
     assert x.dtype == torch.float32 and x.is_contiguous()
@@ -846,14 +849,17 @@ def add_rmsnorm(x, delta, delta_bias, post, weight, eps, offset, out, rows=None)
                                     c_int(dtype_code(delta.dtype) if delta is not None else 0), _ptr(delta_bias), _ptr(pw),
                                     c_float(peps), c_float(poff), _ptr(weight), c_float(eps), c_float(offset), _ptr(out),
                                     c_int(dtype_code(out.dtype) if out is not None else 0), _ptr(rows), c_int(n), c_int(d),
-                                    _stream())
+                                    _stream(), c_float(delta_scale))
     _check(st, "add_rmsnorm", f"rows={n} width={d}")
 
 
-def rope_rows(src, src_col0, src_head_stride, dst, dst_col0, dst_head_stride, positions, heads, width, dims, freqs):
+def rope_rows(src, src_col0, src_head_stride, dst, dst_col0, dst_head_stride, positions, heads, width, dims, freqs,
+              neighbours: bool = False, length: float = 1.0, keep_col0: int = -1, keep_head0: int = 0):
     """In every row and head, ``width`` entries from column ``col0 + head * head_stride`` of ``src`` go to the like
-    place of ``dst``; the first ``dims`` of them rotated in pairs (entry i with entry i + dims/2) by the angle
-    position * freqs[i] (32-bit), the rest as they are.  src and dst may be one buffer."""
+    place of ``dst``; the first ``dims`` of them rotated in pairs (entry i with entry i + dims/2; with ``neighbours``
+    entry 2i with entry 2i + 1) by the angle position * freqs[i] (32-bit), cosine and sine times ``length``, the rest
+    as they are.  src and dst may be one buffer.  With ``keep_col0`` >= 0 the heads from ``keep_head0`` on are also
+    written UNROTATED to ``dst`` at column keep_col0 + (head - keep_head0) * width (columns nothing else touches)."""
     _need_cuda(src, dst, positions, freqs)
     rows = src.shape[0]
     assert src.dtype == dst.dtype and src.stride(1) == 1 and dst.stride(1) == 1 and dst.shape[0] == rows
@@ -861,10 +867,12 @@ def rope_rows(src, src_col0, src_head_stride, dst, dst_col0, dst_head_stride, po
     assert dims == 0 or (freqs.dtype == torch.float32 and freqs.numel() >= dims // 2 and freqs.is_contiguous())
     assert src_col0 + (heads - 1) * src_head_stride + width <= src.shape[1]
     assert dst_col0 + (heads - 1) * dst_head_stride + width <= dst.shape[1]
+    assert keep_col0 < 0 or (0 <= keep_head0 <= heads and keep_col0 + (heads - keep_head0) * width <= dst.shape[1])
     st = kernels().cbis_rope_rows(_ptr(src), c_int(src.stride(0)), c_int(src_col0), c_int(src_head_stride), _ptr(dst),
                                   c_int(dst.stride(0)), c_int(dst_col0), c_int(dst_head_stride), _ptr(positions),
                                   c_int(rows), c_int(heads), c_int(width), c_int(dims), _ptr(freqs),
-                                  c_int(dtype_code(src.dtype)), _stream())
+                                  c_int(dtype_code(src.dtype)), _stream(), c_int(1 if neighbours else 0), c_float(length),
+                                  c_int(keep_col0), c_int(keep_head0))
     _check(st, "rope_rows", f"rows={rows} heads={heads} width={width} dims={dims}")
 
 
@@ -1135,9 +1143,10 @@ def ssm_scan(xbc, proj, dt_off, dt_bias, a_log, d_skip, state, seg_slot, cu_rows
 ROUTE_SCORE = {"sigmoid": 0, "softmax": 1}
 
 
-def route_topk(h, router, top, score, renormalize, ids, weights):
+def route_topk(h, router, top, score, renormalize, ids, weights, renorm_eps: float = 0.0, weight_scale: float = 1.0):
     """Router logits ``h @ router^T`` in 32-bit, scores by ``score``, the ``top`` largest per row into ``ids``
-    (int32 ``[rows, top]``) with their weights (float32; divided by their sum with ``renormalize``)."""
+    (int32 ``[rows, top]``) with their weights (float32; divided by their sum + ``renorm_eps`` with ``renormalize``;
+    then times ``weight_scale``)."""
     _need_cuda(h, router, ids, weights)
     rows, W = h.shape
     E = router.shape[0]
@@ -1146,7 +1155,7 @@ def route_topk(h, router, top, score, renormalize, ids, weights):
     assert ids.shape == (rows, top) and weights.shape == (rows, top)
     st = kernels().cbis_route_topk(_ptr(h), c_int(h.stride(0)), _ptr(router), _ptr(ids), _ptr(weights), c_int(rows),
                                    c_int(W), c_int(E), c_int(top), c_int(ROUTE_SCORE[score]), c_int(1 if renormalize else 0),
-                                   c_int(dtype_code(h.dtype)), _stream())
+                                   c_int(dtype_code(h.dtype)), _stream(), c_float(renorm_eps), c_float(weight_scale))
     _check(st, "route_topk", f"rows={rows} experts={E} top={top}")
 
 

@@ -40,8 +40,12 @@ class Layer:
         self.post_norm_mixer = make_norm(spec.post_norm_mixer) if spec.post_norm_mixer is not None else None
         self.post_norm_feed_forward = (make_norm(spec.post_norm_feed_forward)
                                        if spec.post_norm_feed_forward is not None else None)
+        self.side = make_feed_forward(spec.side) if spec.side is not None else None
+        extra = {}
+        if spec.residual_scale != 1.0 or self.side is not None:
+            extra = {"residual_scale": spec.residual_scale, "side": self.side}
         self.block = make_block(spec.arrangement, self.mixer, self.feed_forward, self.norm_mixer,
-                                self.norm_feed_forward, self.post_norm_mixer, self.post_norm_feed_forward)
+                                self.norm_feed_forward, self.post_norm_mixer, self.post_norm_feed_forward, **extra)
         self.norm_names = tuple(spec.norm_prefixes)
         self.post_norm_names = tuple(spec.post_norm_prefixes)
 
@@ -53,6 +57,8 @@ class Layer:
             out.append((p + self.post_norm_names[0], self.post_norm_mixer))
         if self.post_norm_feed_forward is not None:
             out.append((p + self.post_norm_names[1], self.post_norm_feed_forward))
+        if self.side is not None:
+            out.append((p, self.side))
         return out
 
 
@@ -118,6 +124,8 @@ class Model:
         for li in self.spec.schedule:
             layer = self.layers[li]
             order += layer.mixer.streamed_weights() + layer.feed_forward.streamed_weights()
+            if layer.side is not None:
+                order += layer.side.streamed_weights()
         ops.add_weight_order(order + self.head_part.streamed_weights())
 
     def weight_bytes(self) -> int:

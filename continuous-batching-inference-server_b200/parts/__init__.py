@@ -3,9 +3,9 @@ from .base import (AttentionLike, Block, CacheArray, CacheNeed, Delta, Embedding
                    make_norm, make_position, register_block, register_embedding, register_feed_forward,
                    register_head, register_mixer, register_norm, register_position)
 from . import (attention, blocks, dense, embedding, gated_attention, head, latent_attention, layernorm,  # noqa: F401
-               matrix_memory, positions, retention, rmsnorm, rotary_attention, routed, state_space)  # (importing them registers the built-in kinds)
+               matrix_memory, positions, retention, rmsnorm, rotary_attention, routed, state_space, token_input)  # (importing them registers the built-in kinds)
 from .attention import PagedAttention
-from .blocks import ParallelBlock, PreNormBlock, SandwichBlock
+from .blocks import ParallelBlock, PreNormBlock, SandwichBlock, ScaledPreNormBlock
 from .dense import DenseFeedForward, GatedFeedForward, NoFeedForward
 from .gated_attention import GatedAttention
 from .latent_attention import LatentAttention
@@ -13,7 +13,8 @@ from .matrix_memory import MatrixMemoryMixer
 from .retention import RetentionMixer
 from .rmsnorm import RMSNorm
 from .rotary_attention import RotaryAttention
-from .rotation import rotary_frequencies
+from .rotation import blended_frequencies, rotary_frequencies
+from .token_input import TokenGatedInput
 from .routed import RoutedFeedForward
 from .state_space import StateSpaceMixer
 from .embedding import TokenTable

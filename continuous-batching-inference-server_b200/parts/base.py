@@ -31,10 +31,13 @@ class Delta:
     """What a mixer or feed-forward adds to the residual stream: value (+ bias per column).  ``post``: a norm that
     value + bias passes BEFORE it is added (set by a block with norms after its parts); the norm that adds the
     delta applies it in the same pass if it can (``Norm.takes_post``), else it is applied on its own
-    (``settle_delta``)."""
+    (``settle_delta``).  ``scale``: a constant on everything that is added (after ``post``), for a block that
+    multiplies its parts' results before they join the stream; applied by the norm that adds the delta
+    (``Norm.takes_scale``) or on its own."""
     value: torch.Tensor
     bias: Optional[torch.Tensor] = None
     post: Optional["Norm"] = None
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -160,6 +163,8 @@ class FeedForward(Part):
 
 
 class Norm(Part):
+    takes_scale = False        # whether ``forward`` applies a delta's ``scale`` itself, in its one pass
+
     def forward(self, ctx, x: torch.Tensor, delta: Optional[Delta], rows: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """Adds ``delta`` to the residual stream ``x`` in place (32-bit), returns norm(x) in the
@@ -224,10 +229,28 @@ class Head(Part):
 
 
 def settle_delta(ctx, norm: Norm, delta: Optional[Delta]) -> Optional[Delta]:
-    """What ``norm`` can add as it is: a delta whose own norm ``norm`` does not apply in its pass gets it here."""
-    if delta is None or delta.post is None or norm.takes_post(delta.post):
+    """What ``norm`` can add as it is: a delta whose own norm, or whose scale, ``norm`` does not apply in its pass gets
+    them here."""
+    if delta is None:
+        return None
+    if delta.post is not None and not norm.takes_post(delta.post):
+        delta = Delta(delta.post.apply(ctx, delta.value, delta.bias), scale=delta.scale)
+    if delta.scale != 1.0 and not norm.takes_scale:
+        delta = plain_delta(ctx, delta)
+    return delta
+
+
+def plain_delta(ctx, delta: Delta) -> Delta:
+    """The same addition with nothing left to apply: norm(value + bias) * scale as 32-bit rows."""
+    from ..kernels import ops
+    if delta.post is None and delta.scale == 1.0:
         return delta
-    return Delta(delta.post.apply(ctx, delta.value, delta.bias))
+    out = torch.zeros(delta.value.shape, dtype=torch.float32, device=delta.value.device)
+    post = delta.post.as_rmsnorm() if delta.post is not None else None
+    if delta.post is not None and post is None:
+        return plain_delta(ctx, Delta(delta.post.apply(ctx, delta.value, delta.bias), scale=delta.scale))
+    ops.add_rmsnorm(out, delta.value, delta.bias, post, None, 0.0, 0.0, None, delta_scale=delta.scale)
+    return Delta(out)
 
 
 class Block:
@@ -327,9 +350,11 @@ def make_head(spec) -> Head:
 
 
 def make_block(kind: str, mixer, feed_forward, norm_mixer, norm_feed_forward, post_norm_mixer=None,
-               post_norm_feed_forward=None) -> Block:
+               post_norm_feed_forward=None, **extra) -> Block:
+    """``extra``: what only some arrangements take (a constant on what is added, a third part); an arrangement that
+    does not know a name refuses it."""
     if kind not in _BLOCKS:
         raise KeyError(f"unknown block arrangement {kind!r}; known: {sorted(_BLOCKS)}")
     if post_norm_mixer is None and post_norm_feed_forward is None:
-        return _BLOCKS[kind](mixer, feed_forward, norm_mixer, norm_feed_forward)
-    return _BLOCKS[kind](mixer, feed_forward, norm_mixer, norm_feed_forward, post_norm_mixer, post_norm_feed_forward)
+        return _BLOCKS[kind](mixer, feed_forward, norm_mixer, norm_feed_forward, **extra)
+    return _BLOCKS[kind](mixer, feed_forward, norm_mixer, norm_feed_forward, post_norm_mixer, post_norm_feed_forward, **extra)

@@ -7,15 +7,14 @@ import torch
 
 from ..kernels import ops
 from .attention import PagedAttention
-from .base import Block, Delta, register_block, settle_delta
+from .base import Block, Delta, plain_delta, register_block, settle_delta
 from .dense import DenseFeedForward, NoFeedForward
-from .layernorm import LayerNorm
+from .layernorm import LayerNorm, NoNorm
 
 
 def _add_pending(ctx, x, d) -> None:
     """x += what a layer left pending (through the delta's own norm first, if it names one)."""
-    if d.post is not None:
-        d = Delta(d.post.apply(ctx, d.value, d.bias))
+    d = plain_delta(ctx, d)
     ops.add_delta(x, d.value, d.bias)
 
 
@@ -176,8 +175,8 @@ class SandwichBlock(Block):
     def _after(self, ctx, d, post):
         if d is None or post is None:
             return d
-        if d.post is not None:         # a part that already named a norm of its own: that one first
-            d = Delta(d.post.apply(ctx, d.value, d.bias))
+        if d.post is not None or d.scale != 1.0:   # a part that already named a norm of its own: that one first
+            d = plain_delta(ctx, d)
         return Delta(d.value, d.bias, post)
 
     def forward(self, ctx, x, pending, cache, state):
@@ -189,6 +188,43 @@ class SandwichBlock(Block):
         return self._after(ctx, self.feed_forward.forward(ctx, h), self.post_norm_feed_forward)
 
 
+class ScaledPreNormBlock(Block):
+    """x += m mixer(norm_1(x)); x += m feed_forward(norm_2(x)); and, in a layer that has a third part (``side``: a
+    feed-forward kind that reads the residual stream AS IT IS, for instance a token's own input of the layer),
+    x += m side(x).  ``residual_scale`` m is a constant of the model.  Nothing is added on its own: a part's result is
+    handed on with the constant (``Delta.scale``) and, for a part that names one, its own norm (``Delta.post``), and
+    the norm before the next part adds it in its pass.  With m = 1 a part may add into the stream itself
+    (``ctx.residual``), as in ``PreNormBlock``.  A layer without a feed-forward skips the second line."""
+
+    def __init__(self, mixer, feed_forward, norm_mixer, norm_feed_forward, residual_scale: float = 1.0, side=None):
+        super().__init__(mixer, feed_forward, norm_mixer, norm_feed_forward)
+        self.residual_scale, self.side = float(residual_scale), side
+        self.as_it_is = NoNorm(norm_mixer.width) if side is not None else None
+
+    def _scaled(self, d):
+        if d is None or self.residual_scale == 1.0:
+            return d
+        return Delta(d.value, d.bias, d.post, d.scale * self.residual_scale)
+
+    def _run(self, ctx, x, part, *args):
+        ctx.residual = x if self.residual_scale == 1.0 else None
+        d = part.forward(ctx, *args)
+        ctx.residual = None
+        return self._scaled(d)
+
+    def forward(self, ctx, x, pending, cache, state):
+        h = self.norm_mixer.forward(ctx, x, pending)
+        d = self._run(ctx, x, self.mixer, h, cache, state)
+        if not isinstance(self.feed_forward, NoFeedForward):
+            h = self.norm_feed_forward.forward(ctx, x, d)
+            d = self._run(ctx, x, self.feed_forward, h)
+        if self.side is not None:
+            h = self.as_it_is.forward(ctx, x, d)       # adds what is pending; the rows go on unnormalised
+            d = self._run(ctx, x, self.side, h)
+        return d
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("pre_norm_scaled", ScaledPreNormBlock)
 register_block("parallel", ParallelBlock)
 register_block("sandwich", SandwichBlock)

@@ -11,23 +11,33 @@ from .base import Delta, FeedForward, register_feed_forward
 class DenseFeedForward(FeedForward):
     """act(h @ W1 + b1) @ W2 + b2 with the activation taken on the 32-bit sum
     (reference: python/model.py:50, src/transformer.cpp:86-88).  Weights come in GPT-2's
-    Conv1D layout [in, out] and are kept transposed, [out, in]."""
+    Conv1D layout [in, out] and are kept transposed, [out, in].
+
+    ``plain`` True is the other storage: the two matrices as ``[out, in]`` under the very names ``names`` gives
+    (no ``.weight``), and no biases."""
 
     def __init__(self, width: int, inner: int, activation: str,
-                 names=("mlp.c_fc", "mlp.c_proj")):
+                 names=("mlp.c_fc", "mlp.c_proj"), plain: bool = False):
         if activation not in ops.ACT:
             raise ValueError(f"activation {activation!r} is not one of {sorted(k for k in ops.ACT if k)}")
         self.width, self.inner, self.activation = int(width), int(inner), activation
         self.fc, self.proj = names
+        self.plain = bool(plain)
         self.w1 = self.b1 = self.w2 = self.b2 = None
 
     def tensors(self, prefix):
+        if self.plain:
+            return [TensorDecl(prefix + self.fc, (self.inner, self.width)), TensorDecl(prefix + self.proj, (self.width, self.inner))]
         return [TensorDecl(f"{prefix}{self.fc}.weight", (self.width, self.inner)),
                 TensorDecl(f"{prefix}{self.fc}.bias", (self.inner,), "vector"),
                 TensorDecl(f"{prefix}{self.proj}.weight", (self.inner, self.width)),
                 TensorDecl(f"{prefix}{self.proj}.bias", (self.width,), "vector")]
 
     def load(self, prefix, tensors, dtype, device):
+        if self.plain:
+            self.w1 = self._matrix(tensors[prefix + self.fc], dtype, device)
+            self.w2 = self._matrix(tensors[prefix + self.proj], dtype, device)
+            return
         self.w1 = self._matrix_nk(tensors[f"{prefix}{self.fc}.weight"], dtype, device)
         self.b1 = self._vector(tensors[f"{prefix}{self.fc}.bias"], device)
         self.w2 = self._matrix_nk(tensors[f"{prefix}{self.proj}.weight"], dtype, device)
@@ -37,7 +47,7 @@ class DenseFeedForward(FeedForward):
         return [self.w1, self.w2]
 
     def fuses_norm(self, ctx, norm):
-        return ops.ln_linear_takes(ctx, norm, self.w1) and self.inner % 8 == 0
+        return not self.plain and ops.ln_linear_takes(ctx, norm, self.w1) and self.inner % 8 == 0
 
     def forward_residual(self, ctx, x, norm):
         a = torch.empty((ctx.n_rows, self.inner), dtype=ctx.dtype, device=x.device)
@@ -46,7 +56,10 @@ class DenseFeedForward(FeedForward):
 
     def forward(self, ctx, h):
         a = ops.linear(h, self.w1, self.b1, self.activation)
-        if ops.linear_add_takes(a, self.w2, ctx.residual):         # the product adds into the residual stream itself
+        if self.b2 is None:
+            if ops.linear_residual(a, self.w2, ctx.residual):
+                return None
+        elif ops.linear_add_takes(a, self.w2, ctx.residual):       # the product adds into the residual stream itself
             ops.linear_add(a, self.w2, self.b2, ctx.residual)
             return None
         return Delta(ops.linear(a, self.w2, None, None, out_dtype=torch.float32), self.b2)
@@ -105,6 +118,17 @@ class GatedFeedForward(FeedForward):
             ops.linear_add(a, self.w_down, self.b_down, ctx.residual)
             return None
         return Delta(ops.linear(a, self.w_down, None, None, out_dtype=torch.float32), self.b_down)
+
+
+    def forward_into(self, h, out) -> None:
+        """out += this feed-forward of h; ``out``: 32-bit rows (another part's result that this one joins)."""
+        F = self.inner
+        gu = ops.linear(h, self.w_gate_up, self.b_gate_up)
+        a = torch.empty((h.shape[0], F), dtype=h.dtype, device=h.device)
+        ops.gate_mul(gu[:, :F], gu[:, F:], self.activation, a)
+        if self.b_down is None and ops.linear_residual(a, self.w_down, out):
+            return
+        ops.add_delta(out, ops.linear(a, self.w_down, None, None, out_dtype=torch.float32), self.b_down)
 
 
 class NoFeedForward(FeedForward):

@@ -57,12 +57,18 @@ class NoNorm(Norm):
         return (getattr(post, "width", None) == self.width and self.width <= ops.RMS_RESIDUAL_MAX_WIDTH
                 and post.as_rmsnorm() is not None)
 
+    @property
+    def takes_scale(self):
+        return self.width <= ops.RMS_RESIDUAL_MAX_WIDTH
+
     def forward(self, ctx, x, delta: Optional[Delta], rows=None, out_dtype=None):
         n = rows.shape[0] if rows is not None else x.shape[0]
         delta = settle_delta(ctx, self, delta)
         out = torch.empty((n, self.width), dtype=out_dtype or ctx.dtype, device=x.device)
-        if delta is not None and delta.post is not None:      # x += post(delta); the rows go on as they are
-            ops.add_rmsnorm(x, delta.value, delta.bias, delta.post.as_rmsnorm(), None, 0.0, 0.0, out, rows)
+        if delta is not None and (delta.post is not None or delta.scale != 1.0):
+            # x += post(delta) * scale; the rows go on as they are
+            ops.add_rmsnorm(x, delta.value, delta.bias, delta.post.as_rmsnorm() if delta.post is not None else None,
+                            None, 0.0, 0.0, out, rows, delta_scale=delta.scale)
             return out
         ops.add_layernorm(x, delta.value if delta else None, delta.bias if delta else None, None, None, 0.0, out, rows)
         return out

@@ -32,6 +32,8 @@ class RMSNorm(Norm):
     def load(self, prefix, tensors, dtype, device):
         self.weight = self._vector(tensors[prefix + self.name], device)
 
+    takes_scale = True
+
     def as_rmsnorm(self):
         return (self.weight, self.eps, self.offset) if self.weight is not None else None
 
@@ -46,7 +48,7 @@ class RMSNorm(Norm):
         if delta is not None and delta.post is not None:
             post = (delta.post.weight, delta.post.eps, delta.post.offset)
         ops.add_rmsnorm(x, delta.value if delta else None, delta.bias if delta else None, post, self.weight, self.eps,
-                        self.offset, out, rows)
+                        self.offset, out, rows, delta_scale=delta.scale if delta else 1.0)
         return out
 
     def apply(self, ctx, value, bias=None):
