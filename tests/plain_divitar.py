@@ -106,13 +106,13 @@ def rotate_neighbours(x, positions, freqs, dims, length=1.0):
 
 # ---- which keys a query sees ---------------------------------------------------------------------------------------
 def sees_block(i, j, size):
-    """Keys of the query's own block of ``size`` positions, up to itself."""
-    return j <= i and i // size == j // size
+    """Keys of the query's own block of ``size`` positions, up to itself (``size`` 0: all keys up to itself)."""
+    return j <= i and (size == 0 or i // size == j // size)
 
 
 def sees_window(i, j, size):
-    """The query itself and the size - 1 positions before it."""
-    return 0 <= i - j < size
+    """The query itself and the size - 1 positions before it (``size`` 0: all before it)."""
+    return 0 <= i - j and (size == 0 or i - j < size)
 
 
 def softmax_rows(scores, positions, sees, sink=None):
@@ -134,16 +134,17 @@ def softmax_rows(scores, positions, sees, sink=None):
 def attention(m, tensors, prefix, h, positions):
     T = h.shape[0]
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
-    rot = m["rot"]
+    rot = m.get("rot")
     q = linear(h, tensors, prefix + "mix.q", bias=True).reshape(T, H, D)
     k = linear(h, tensors, prefix + "mix.k", bias=True).reshape(T, G, D)
     v = k.copy()                                  # the values are the keys as projected
-    factor = (rot.get("scaling") or {}).get("factor", 1.0)
-    freqs = divided_frequencies(rot["base"], rot["dims"], factor)
-    q = rotate_half(q, positions, freqs, rot["dims"])
-    k = rotate_half(k, positions, freqs, rot["dims"])
+    if rot is not None and rot["dims"]:
+        factor = (rot.get("scaling") or {}).get("factor", 1.0)
+        freqs = divided_frequencies(rot["base"], rot["dims"], factor)
+        q = rotate_half(q, positions, freqs, rot["dims"])
+        k = rotate_half(k, positions, freqs, rot["dims"])
     gate = sigmoid(linear(h, tensors, prefix + "mix.g"))          # [T, H]
-    size = m["mask"]["size"]
+    size = (m.get("mask") or {}).get("size", 0)
     out = np.zeros((T, H, D))
     for head in range(H):
         g = head // (H // G)
@@ -155,9 +156,11 @@ def attention(m, tensors, prefix, h, positions):
 
 def latent_and_key_part(m, tensors, prefix, h, positions, eps):
     """What a layer with a down-projection of its own caches per token: the normalised latent and the rotated part."""
-    R, P = m["kv_rank"], m["rot_dim"]
+    R, P = m["kv_rank"], m.get("rot_dim", 0)
     ckv = linear(h, tensors, prefix + "mix.dkv")
     c = rms_norm(ckv[:, :R], tensors[prefix + "mix.dkv.norm"], eps)
+    if not P:
+        return c, np.zeros((h.shape[0], 0))
     freqs, length = latent_rotation(m)
     kr = rotate_neighbours(ckv[:, None, R:R + P], positions, freqs, m["rot"]["dims"], length)[:, 0]
     return c, kr
@@ -174,14 +177,16 @@ def latent_rotation(m):
 def latent_attention(m, tensors, prefix, h, positions, c, kr):
     """``c`` [T, rank] and ``kr`` [T, rot_dim]: the latents and rotated key parts (this layer's or another's)."""
     T = h.shape[0]
-    H, D, P, V, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    H, D, P, V, R = m["heads"], m["dim"], m.get("rot_dim", 0), m["vdim"], m["kv_rank"]
     q = linear(h, tensors, prefix + "mix.q").reshape(T, H, D + P)
-    freqs, length = latent_rotation(m)
-    qr = rotate_neighbours(q[:, :, D:], positions, freqs, m["rot"]["dims"], length)
+    qr = q[:, :, D:]
+    if P:
+        freqs, length = latent_rotation(m)
+        qr = rotate_neighbours(qr, positions, freqs, m["rot"]["dims"], length)
     k = linear(c, tensors, prefix + "mix.uk").reshape(T, H, D)
     v = linear(c, tensors, prefix + "mix.uv").reshape(T, H, V)
     sinks = np.asarray(tensors[prefix + "mix.sink"], dtype=np.float64)
-    size = m["mask"]["size"]
+    size = (m.get("mask") or {}).get("size", 0)
     out = np.zeros((T, H, V))
     for head in range(H):
         scores = (q[:, head, :D] @ k[:, head].T + qr[:, head] @ kr.T) * m["scale"]
@@ -268,3 +273,18 @@ def forward(cfg, tensors, tokens, positions=None):
     h = rms_norm(x, tensors["final.norm"], eps)
     logits = linear(h, tensors, "head") * cfg.get("logit_scale", 1.0)
     return logits, np.stack(streams), gaps
+
+
+def attention_rows(q, k, v, scale, sees, sinks=None, positions=None):
+    """Attention alone: q [T, H, D], k [T, G, D], v [T, G, V] of one sequence; ``sees(i, j)`` says which keys the
+    query at position i takes; ``sinks`` [H] join the denominators.  Returns [T, H, V]."""
+    q, k, v = (np.asarray(a, dtype=np.float64) for a in (q, k, v))
+    T, H, _ = q.shape
+    G = k.shape[1]
+    positions = list(range(T)) if positions is None else list(positions)
+    out = np.zeros((T, H, v.shape[2]))
+    for head in range(H):
+        g = head // (H // G)
+        w = softmax_rows((q[:, head] @ k[:, g].T) * scale, positions, sees, None if sinks is None else float(sinks[head]))
+        out[:, head] = w @ v[:, g]
+    return out
