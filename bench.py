@@ -115,14 +115,15 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl", "batching", "vekedra", "figotar", "vatevik"],
+    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl", "batching", "vekedra", "figotar", "vatevik", "divitar"],
                     help="1.3b: the default measurement; 6.7b: batch-64 decode at context 2,048; "
                          "xl: 64 mixed requests through the scheduler (prompts 32-768, 256 outputs each); "
                          "batching: the reference's own workload at the reference's own sizes (both --impl arms); "
                          "vekedra: prefill and decode of the Vekedra design at two layer sizes beside the GPT-2 style model "
                          "of equal width and depth, and its own kernels one by one against their bytes; "
                          "figotar: the same for the Figotar design, beside Vekedra and the GPT-2 style model; "
-                         "vatevik: the same for the Vatevik design, beside Figotar and the GPT-2 style model")
+                         "vatevik: the same for the Vatevik design, beside Figotar and the GPT-2 style model; "
+                         "divitar: the same for the Divitar design, beside Figotar, Vekedra and the GPT-2 style model")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
@@ -161,6 +162,8 @@ def main() -> int:
         return figotar_workload(args, cb, torch)
     if args.config == "vatevik":
         return vatevik_workload(args, cb, torch)
+    if args.config == "divitar":
+        return divitar_workload(args, cb, torch)
     if args.config == "6.7b":
         args.skip_points = True
         args.batch = args.batch or 64
@@ -680,6 +683,199 @@ def vatevik_workload(args, cb, torch) -> int:
             "kernels": vatevik_kernels(torch, ops, pk), "clocks": clocks, "peaks": pk}
     print(json.dumps(line))
     return 0
+
+
+def divitar_sizes(width, layers):
+    """A Divitar configuration with layers of the sizes a model of this width would have: of every four layers a latent
+    attention that keeps its latents, an attention inside blocks of positions (grouped key/value heads), a latent
+    attention that reads the first one's latents, and another block attention; dense and routed feed-forwards (with an
+    expert for all) in turn; a second token table of 64 columns a layer."""
+    big = width >= 2048
+    hd = 128 if big else 64
+    heads = width // hd
+    att = {"dim": hd, "heads": heads, "kv_heads": max(1, heads // 4), "mask": {"size": 1024 if big else 512},
+           "rot": {"base": 10000.0, "dims": hd, "scaling": {"factor": 4.0}}, "scale": hd ** -0.5, "vdim": hd}
+    lat = {"dim": 64, "heads": 16, "kv_rank": 64, "mask": {"size": 1024 if big else 512}, "rot_dim": 64,
+           "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+           "scale": 128 ** -0.5, "vdim": 64}
+    dense = {"kind": "dense", "ff": 4 * width}
+    moe = {"kind": "moe", "expert": {"ff": 11 * width // 16}, "router": {"experts": 16 if big else 8, "scale": 2.5, "top": 2},
+           "shared": {"ff": 11 * width // 16}}
+    out = []
+    for i in range(layers):
+        kind = ("latent_attention", "attention")[i % 2]
+        mixer = dict(lat if kind == "latent_attention" else att)
+        if i % 4 == 2:
+            mixer["kv_from"] = i - 2
+        out.append({"type": kind, "mixer": mixer, "mlp": dict(dense if i % 4 == 0 else moe)})
+    return {"architecture": "Divitar", "layers": out, "logit_scale": 0.5, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "token_side": {"dim": 64}, "vocab": 32000, "width": width}
+
+
+def divitar_workload(args, cb, torch) -> int:
+    """Prefill (one 2,048-token prompt in one step) and decode (batch 8 from context 1,024, the captured step with
+    argmax on the device) of the Divitar design at two layer sizes, each beside Figotar (the closest model in its
+    mixers: gated attention over grouped heads, attention over a latent with a rotated key part and a sink), Vekedra
+    (the closest in its feed-forwards: routed experts) and the GPT-2 style model of equal width and depth; then the
+    design's own kernels alone, at the larger size, beside the like kernels of those models."""
+    from cbis_b200.kernels import ops
+    pk = peaks()
+    P, T, B = 2048, 2048, args.batch or 8
+    steps, warm = min(args.steps, 128), max(3, min(args.warmup, 8))
+    layers = args.layers or 8
+    gen = torch.Generator().manual_seed(0)
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    for width in (1024, 2048):
+        gpt = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=layers, n_embd=width, n_head=16,
+                   n_inner=4 * width, vocab_size=32000, n_positions=P, activation_function="gelu",
+                   layer_norm_epsilon=1e-5, tie_word_embeddings=False)
+        sizes[f"width_{width}"] = {name: measure_model(args, cb, torch, pk, cfgd, 32000, B, P, T, steps, warm, gen)
+                                   for name, cfgd in (("divitar", divitar_sizes(width, layers)),
+                                                      ("figotar", figotar_sizes(width, layers)),
+                                                      ("vekedra", vekedra_sizes(width, layers)), ("gpt2_style", gpt))}
+    clocks = sampler.stop()
+    line = {"metric": f"Divitar prefill and decode tokens/s beside Figotar, Vekedra and the GPT-2 style model of equal "
+                      f"width and depth ({layers} layers, batch {B}, prompt {T})", "unit": "tokens/s", "n_gpus": 1,
+            "impl": "b200", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+            "higher_is_better": True, "value": sizes["width_2048"]["divitar"]["decode_tokens_per_s"], "sizes": sizes,
+            "kernels": divitar_kernels(torch, ops, pk), "clocks": clocks, "peaks": pk}
+    print(json.dumps(line))
+    return 0
+
+
+def divitar_kernels(torch, ops, pk):
+    """Microseconds of the kernels the design added or changed, alone, at the layer sizes of width 2,048, with the bytes
+    each has to move over its time as a fraction of the measured copy bandwidth (attention over prompts: its
+    arithmetic as a fraction of the measured bf16 peak), each beside the like kernel of the closest model at equal
+    sizes."""
+    bf = torch.bfloat16
+    out = {}
+    timed = graph_timer(torch, pk, out)
+    W, nh, nkv, hd = 2048, 16, 4, 128              # block attention of width 2,048
+    lh, rank, rot = 16, 64, 64                     # latent attention: 16 heads over cached rows of 64 + 64
+    E, top, side = 16, 2, 64
+    freqs = (10000.0 ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().cuda()
+    for rows, segs, tag in ((2048, 1, "prefill_2048"), (8, 8, "decode_8")):
+        per = rows // segs
+        pos = (torch.arange(rows, dtype=torch.int32, device="cuda") % per) + (1024 if segs > 1 else 0)
+        dq, dk = nh * hd, nkv * hd
+
+        def rope_keep():        # q | k | gate -> q and k rotated, the keys once more as the values
+            src = torch.randn(rows, dq + dk + nh, device="cuda").to(bf)
+            dst = torch.empty(rows, dq + 2 * dk, dtype=bf, device="cuda")
+            return lambda: ops.rope_rows(src, 0, hd, dst, 0, hd, pos, nh + nkv, hd, hd, freqs, keep_col0=dq + dk, keep_head0=nh)
+        timed(rope_keep, rows * (2 * (dq + dk) + dk) * 2, f"rope_rows_keys_kept_as_values_{tag}")
+
+        def rope_alone():
+            buf = torch.randn(rows, dq + dk, device="cuda").to(bf)
+            return lambda: ops.rope_rows(buf, 0, hd, buf, 0, hd, pos, nh + nkv, hd, hd, freqs)
+        timed(rope_alone, rows * 2 * (dq + dk) * 2, f"closest_model_rope_rows_{tag}")
+
+        def rope_neighbours():  # the rotated query parts of the latent attention, moved behind the latent-space queries
+            q = torch.randn(rows, lh * (64 + rot), device="cuda").to(bf)
+            qc = torch.empty(rows, lh * (rank + rot), dtype=bf, device="cuda")
+            return lambda: ops.rope_rows(q, 64, 64 + rot, qc, rank, rank + rot, pos, lh, rot, rot, freqs, neighbours=True, length=1.14)
+        timed(rope_neighbours, rows * 2 * lh * rot * 2, f"rope_rows_neighbours_{tag}")
+
+        def rope_half():
+            q = torch.randn(rows, lh * (64 + rot), device="cuda").to(bf)
+            qc = torch.empty(rows, lh * (rank + rot), dtype=bf, device="cuda")
+            return lambda: ops.rope_rows(q, 64, 64 + rot, qc, rank, rank + rot, pos, lh, rot, rot, freqs)
+        timed(rope_half, rows * 2 * lh * rot * 2, f"closest_model_rope_rows_half_{tag}")
+
+        def scaled_add():
+            x, d = torch.randn(rows, W, device="cuda"), torch.randn(rows, W, device="cuda")
+            w = torch.ones(W, device="cuda")
+            o = torch.empty(rows, W, dtype=bf, device="cuda")
+            return lambda: ops.add_rmsnorm(x, d, None, None, w, 1e-6, 0.0, o, delta_scale=0.5)
+        timed(scaled_add, rows * W * (4 + 4 + 4 + 2), f"add_rmsnorm_scaled_{tag}")
+
+        def side_add():         # the token input's result through its own norm, scaled, the rows handed on for the next norm
+            x, d = torch.randn(rows, W, device="cuda"), torch.randn(rows, W, device="cuda")
+            w, wp = torch.ones(W, device="cuda"), torch.ones(W, device="cuda")
+            o = torch.empty(rows, W, dtype=bf, device="cuda")
+            return lambda: ops.add_rmsnorm(x, d, None, (wp, 1e-6, 0.0), w, 1e-6, 0.0, o, delta_scale=0.5)
+        timed(side_add, rows * W * (4 + 4 + 4 + 2), f"add_rmsnorm_scaled_with_the_result_normalised_{tag}")
+
+        def sandwich():
+            x, d = torch.randn(rows, W, device="cuda"), torch.randn(rows, W, device="cuda")
+            w, wb = torch.zeros(W, device="cuda"), torch.zeros(W, device="cuda")
+            o = torch.empty(rows, W, dtype=bf, device="cuda")
+            return lambda: ops.add_rmsnorm(x, d, None, (wb, 1e-6, 1.0), w, 1e-6, 1.0, o)
+        timed(sandwich, rows * W * (4 + 4 + 4 + 2), f"closest_model_add_rmsnorm_{tag}")
+
+        def table_gate():
+            a = torch.randn(rows, side, device="cuda").to(bf)
+            table = torch.randn(32000, side, device="cuda").to(bf)
+            tok = torch.randint(0, 32000, (rows,), device="cuda").int()
+            return lambda: ops.gate_mul(a, table, "gelu_tanh", a, b_rows=tok)
+        timed(table_gate, rows * side * 3 * 2, f"gate_mul_table_rows_{tag}")
+
+        def plain_gate():
+            a, b = torch.randn(rows, side, device="cuda").to(bf), torch.randn(rows, side, device="cuda").to(bf)
+            return lambda: ops.gate_mul(a, b, "gelu_tanh", a)
+        timed(plain_gate, rows * side * 3 * 2, f"closest_model_gate_mul_{tag}")
+
+        def route(scale, eps):
+            def make():
+                h = torch.randn(rows, W, device="cuda").to(bf)
+                r = torch.randn(E, W, device="cuda").to(bf)
+                ids = torch.empty(rows, top, dtype=torch.int32, device="cuda")
+                wt = torch.empty(rows, top, dtype=torch.float32, device="cuda")
+                return lambda: ops.route_topk(h, r, top, "sigmoid", scale != 1.0, ids, wt, eps, scale)
+            return make
+        timed(route(2.5, 1e-20), rows * W * 2 + E * W * 2, f"route_topk_renormalised_scaled_{tag}")
+        timed(route(1.0, 0.0), rows * W * 2 + E * W * 2, f"closest_model_route_topk_{tag}")
+
+        def product(act):
+            def make():
+                x = torch.randn(rows, W, device="cuda").to(bf)
+                w = (torch.randn(4 * W, W, device="cuda") * W ** -0.5).to(bf)
+                return lambda: ops.linear(x, w, None, act)
+            return make
+        flops = 2.0 * rows * W * 4 * W
+        timed(product("relu2"), (rows * W + 4 * W * W + rows * 4 * W) * 2, f"up_product_relu_squared_{tag}", flops=flops)
+        timed(product("gelu_tanh"), (rows * W + 4 * W * W + rows * 4 * W) * 2, f"closest_model_up_product_gelu_{tag}", flops=flops)
+
+    # attention of 16 query heads over 4 key/value heads of 128 inside blocks of 1,024 positions, beside the same
+    # kernels with a sliding window of 1,024 and with every key; pages of 16
+    ps, ctx_len, size = 16, 2048, 1024
+    pages = ctx_len // ps
+    bt1 = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, pages)
+    cu1 = torch.tensor([0, ctx_len], dtype=torch.int32, device="cuda")
+    zero1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def seen(mask):
+        def first(p):
+            return max(0, p - mask + 1) if mask > 0 else (p - p % -mask if mask < 0 else 0)
+        return sum(p - first(p) + 1 for p in range(ctx_len))
+    for name, mask in (("attention_prefill_2048_blocks_of_1024", -size), ("closest_model_attention_prefill_2048_window_1024", size),
+                       ("attention_prefill_2048_every_key", 0)):
+        def prefill():
+            q = torch.randn(ctx_len, nh * hd, device="cuda").to(bf)
+            k, v = (torch.randn(pages, nkv, ps, hd, device="cuda").to(bf) for _ in range(2))
+            o = torch.empty(ctx_len, nh * hd, dtype=bf, device="cuda")
+            return lambda: ops.paged_prefill_tc5(q, k, v, bt1, cu1, zero1, o, 0, 1, ctx_len, nh, nkv, hd, ps, hd ** -0.5, mask)
+        timed(prefill, ctx_len * (2 * nh + 2 * nkv) * hd * 2, name, flops=4.0 * seen(mask) * nh * hd)
+    B = 8
+    btB = torch.arange(B * pages, dtype=torch.int32, device="cuda").view(B, pages)
+    row_seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    posB = torch.full((B,), ctx_len - 1, dtype=torch.int32, device="cuda")
+    slot_map = (btB[:, -1] * ps + ps - 1).contiguous()
+    for name, mask in (("attention_decode_8_blocks_of_1024", -size), ("closest_model_attention_decode_8_window_1024", size)):
+        def decode():
+            qkv = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda").to(bf)
+            k, v = (torch.randn(B * pages, nkv, ps, hd, device="cuda").to(bf) for _ in range(2))
+            o = torch.empty(B, nh * hd, dtype=bf, device="cuda")
+            ns = ops.decode_splits(B, nh, ctx_len)
+            scratch = torch.empty(max(1, ops.decode_scratch_floats(B, nh, hd, ns)), device="cuda")
+            counters = torch.zeros(B * nh, dtype=torch.int32, device="cuda")
+            return lambda: ops.paged_decode_bf16(qkv, nh * hd, (nh + nkv) * hd, k, v, btB, row_seq, posB, slot_map, o, scratch,
+                                                 counters, nh, nkv, hd, ps, hd ** -0.5, mask, ns)
+        timed(decode, B * size * 2 * nkv * hd * 2, name)
+    return out
 
 
 def graph_timer(torch, pk, out):
