@@ -93,6 +93,14 @@ WIDE = config(128, 200, [
     latent(2, 64, 32, 64, 96, 64, 0.1, base=1000.0, scaling=blend(8.0, 64, 16.0, 2.0), kv_from=1, mlp=moe(4, 1, 32)),
 ], mult=0.4, logit_scale=2.0, side=16)
 
+# layers as wide as a small real model's: products of hundreds of rows on the TMA + tcgen05 kernels with their
+# epilogues, routed experts in tiles, head size 64 on the tensor-core attention kernels, a cached row of 128
+REAL = config(512, 1000, [
+    latent(8, 64, 32, 64, 96, 100, 0.1, base=10000.0, scaling=blend(4.0, 256, 16.0, 1.0), mlp=dense(2048)),
+    attn(8, 2, 64, 128, 0.125, factor=4.0, mlp=moe(8, 2, 352, scale=2.0, shared=352)),
+    latent(8, 64, 32, 64, 96, 60, 0.1, base=10000.0, scaling=blend(4.0, 256, 16.0, 1.0), kv_from=0, mlp=moe(8, 2, 352, scale=2.0)),
+], mult=0.5, logit_scale=0.25, side=32)
+
 ONE_LAYER = {
     "attention": config(64, 80, [attn(4, 2, 16, 21, 0.25, base=500.0, rot_dims=12, factor=2.0, mlp=None)], side=None),
     "latent": config(64, 80, [latent(3, 16, 8, 24, 40, 17, 0.2, base=200.0, scaling=blend(2.0, 32, 8.0, 1.0), mlp=None)], side=None),
@@ -100,6 +108,16 @@ ONE_LAYER = {
     "routed": config(64, 80, [attn(2, 2, 8, 0, 0.3, rot_dims=0, mlp=moe(6, 2, 24, scale=1.5, shared=32))], side=None),
     "side": config(64, 80, [attn(2, 2, 8, 0, 0.3, rot_dims=0, mlp=None)], side=12),
 }
+
+
+def unrouted(cfgd):
+    """The configuration with dense feed-forwards in place of its routed ones: for comparisons of chosen tokens in
+    bfloat16, where rounding may send a token to another expert."""
+    out = copy.deepcopy(cfgd)
+    for layer in out["layers"]:
+        if layer["mlp"] is not None and layer["mlp"]["kind"] == "moe":
+            layer["mlp"] = dense(48)
+    return out
 
 
 def make_weights(cfgd, seed, std=0.25, tweak=None):

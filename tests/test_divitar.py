@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_divitar as pd
-from divitar_helpers import (MIXED, ODD, ONE_LAYER, WIDE, as_numpy, assert_close, assert_same, make_engine, make_weights,
+from divitar_helpers import (MIXED, ODD, ONE_LAYER, REAL, WIDE, as_numpy, assert_close, assert_same, make_engine, make_weights,
                              mixed_schedule, plain, plain_all, run_cut, tokens_of)
 
 pytestmark = pytest.mark.gpu
@@ -264,6 +264,20 @@ def test_sizes_of_the_tiled_kernels(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_as_wide_as_a_small_real_model(dtype):
+    """Width 512, a prompt of 300 tokens: the products run on the TMA + tcgen05 kernels (relu squared in the epilogue,
+    results added by the scaled norm), the experts in tiles over rows sorted by expert, attention of head size 64 on the
+    tensor-core kernels for prompts and for decoding."""
+    cfgd = REAL
+    w = make_weights(cfgd, 19, std=0.1)
+    toks = tokens_of(cfgd, 300, 5)
+    ref, _, close = plain_all(cfgd, w, toks)
+    eng = make_engine(cfgd, w, dtype, page_size=16, num_pages=40, max_batched_tokens=512)
+    for sizes in ([300], [150, 2, 148], [270] + [1] * 30):
+        assert_close(run_cut(eng, toks, sizes), ref, dtype, sizes, close, tol32=1e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["mixed", "odd"])
 def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(name, dtype):
     """Six requests through three slots and a pool smaller than the requests together: portions of some beside single
@@ -340,23 +354,27 @@ def test_greedy_generation_through_the_scheduler(dtype):
     that holds less than all of them): the tokens are the plain implementation's greedy choices wherever its two best
     logits are further apart than rounding."""
     import cbis_b200 as cb
-    cfgd = MIXED
+    from divitar_helpers import unrouted
+    cfgd = MIXED if dtype == "float32" else unrouted(MIXED)      # bfloat16: rounding may flip an expert, so none there
     w = make_weights(cfgd, 13)
     prompts = [tokens_of(cfgd, n, 70 + n) for n in (3, 40, 1, 25, 33)]
     new = 12
     eng = make_engine(cfgd, w, dtype, num_pages=24, max_num_seqs=3, max_batched_tokens=64, prefill_chunk=16)
     outs = eng.generate(prompts, cb.SamplingParams(max_new_tokens=new))
     gap = 1e-3 if dtype == "float32" else 0.25
+    checked = 0
     for p, o in zip(prompts, outs):
         assert len(o) == new
         seq = list(p)
         for tok in o:
-            logits, _, close = plain_all(cfgd, w, seq)
-            top2 = torch.topk(logits[-1], 2).values
-            if top2[0] - top2[1] < gap or (dtype == "bfloat16" and close < len(seq)):
+            logits = plain(cfgd, w, seq)[-1]
+            top2 = torch.topk(logits, 2).values
+            if top2[0] - top2[1] < gap:
                 break                                   # a close call: from here on the sequences may part
-            assert tok == int(logits[-1].argmax()), (len(p), len(seq))
+            assert tok == int(logits.argmax()), (len(p), len(seq))
             seq.append(tok)
+            checked += 1
+    assert checked >= 10, checked
     assert eng.scheduler.idle()
     again = eng.generate(prompts[:2], cb.SamplingParams(max_new_tokens=new))     # slots and pages used again
     assert again == outs[:2]
