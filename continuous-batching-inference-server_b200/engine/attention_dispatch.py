@@ -3,7 +3,8 @@
 Rows of one-token segments (decoding) come first, the rows of longer segments (portions of
 prompts) after them, so each kind is one run of rows.  All kernels read the same pages and
 keep the same contract: the query at position p sees the keys of its own request up to p
-(inside the window, if the mixer has one).
+(inside the window, if the mixer has one; a mixer whose ``window`` is negative means blocks of that many
+positions, counted from position 0: the query sees its own block's keys up to p).
 
 * bfloat16, head size a multiple of 8, decoding rows: the split-KV decode kernel, which also
   stores the current token's key and value;

@@ -512,6 +512,8 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, row_seq, positions
                             head_dim, page_size, scale, window=0, chunks=(1, 0), partial=None, v_head_dim=0,
                             slopes=None, sinks=None, q_temp=None):
     """Attention of every row over its request's pages: keys max(0,p-window+1)..p for the query at p.
+    ``window`` is one signed number in every attention kernel: 0 every key up to p; w > 0 a sliding window of w keys;
+    w < 0 the keys of p's own block of -w positions, p - p mod (-w) .. p, blocks counted from position 0.
     ``chunks`` = (n, keys) from ``generic_key_chunks`` cuts every row's keys n ways over as many warps (every
     context below n * keys); ``partial`` then holds ``rows * n_head * n * (head_dim + 4)`` floats.
     ``v_head_dim``: the values' width where it differs from the keys' (``out`` is then ``n_head * v_head_dim`` wide);
