@@ -696,7 +696,7 @@ def divitar_sizes(width, layers):
     att = {"dim": hd, "heads": heads, "kv_heads": max(1, heads // 4), "mask": {"size": 1024 if big else 512},
            "rot": {"base": 10000.0, "dims": hd, "scaling": {"factor": 4.0}}, "scale": hd ** -0.5, "vdim": hd}
     lat = {"dim": 64, "heads": 16, "kv_rank": 64, "mask": {"size": 1024 if big else 512}, "rot_dim": 64,
-           "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+           "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}},
            "scale": 128 ** -0.5, "vdim": 64}
     dense = {"kind": "dense", "ff": 4 * width}
     moe = {"kind": "moe", "expert": {"ff": 11 * width // 16}, "router": {"experts": 16 if big else 8, "scale": 2.5, "top": 2},

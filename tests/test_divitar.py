@@ -36,7 +36,7 @@ def test_rotation_of_neighbours_with_longer_cosines_and_keys_kept_as_they_came(d
     T = 37
     pos = torch.randint(0, 600, (T,), generator=g).int()       # angles are 32-bit: their rounding grows with the position
     tol = 2e-4 if dtype == "float32" else 3e-2
-    for heads, width, dims, neighbours, length in ((3, 16, 16, True, 1.0693), (2, 20, 6, True, 1.0), (1, 8, 8, True, 0.9),
+    for heads, width, dims, neighbours, length in ((3, 16, 16, True, 1.11), (2, 20, 6, True, 1.0), (1, 8, 8, True, 0.9),
                                                    (5, 12, 10, False, 1.25), (2, 6, 0, True, 1.3)):
         x = rounded(torch.randn(T, heads, width, generator=g), dtype)
         freqs = torch.tensor(pd.plain_frequencies(77.0, dims) if dims else [], dtype=torch.float32)
